@@ -1,0 +1,121 @@
+/*
+ * repdl_b200 -- C ABI of the bit-reproducible operator backend for NVIDIA B200 (sm_100a).
+ *
+ * Every entry point replaces one function of microsoft/RepDL's operator backend (the
+ * functions its Python layer binds in backend/cuda/bind.cpp:6-19 and calls from
+ * repdl/ops.py:12-157) and produces, on the GPU, exactly the bits the reference's CPU
+ * backend produces for the same inputs: one fp32 accumulator per output element, updated
+ * in the reference's order with IEEE-754 single-rounding FMA / add, no flush-to-zero, no
+ * tensor cores, no atomics.
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers on the CURRENT device unless a comment says host.
+ *   - Tensors are fp32, row-major / NCHW, dense unless a leading dimension is passed.
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream).
+ *     Calls are asynchronous: they enqueue work and return.
+ *   - Return value: 0 success; negative = invalid argument (REPDL_E_*); positive = the
+ *     cudaError_t reported by the launch.  Nothing throws, nothing allocates device
+ *     memory unless the comment says so; scratch is passed in by the caller.
+ *   - Inputs are never written.  Outputs may not alias inputs.
+ */
+#ifndef REPDL_B200_H
+#define REPDL_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define REPDL_OK 0
+#define REPDL_E_NULL (-1)      /* a required pointer is NULL */
+#define REPDL_E_SHAPE (-2)     /* a dimension is negative or inconsistent */
+#define REPDL_E_RANGE (-3)     /* a size exceeds what the kernel indexes (see each call) */
+#define REPDL_E_SCRATCH (-4)   /* scratch buffer missing or too small */
+#define REPDL_E_UNSUPPORTED (-5)
+
+/* Library version and the compute capability the kernels were compiled for (100). */
+int repdl_b200_version(void);
+int repdl_b200_sm_arch(void);
+/* Human-readable text for a status returned by any call below (static storage). */
+const char *repdl_b200_strerror(int status);
+
+/* ---- matrix multiplication -------------------------------------------------------------
+ * Replaces repdl::cuda::matrix_multiplication::mm (backend/cuda/matrix_multiplication.cu:234-260),
+ * bits defined by backend/cpu/matrix_multiplication.cpp:12-36:
+ *     C[i][j] = fold over k = 0..K-1 ascending of fmaf(opA(i,k), opB(k,j), .), starting at +0
+ * opA(i,k) = transA ? A[k*lda+i] : A[i*lda+k];  opB(k,j) = transB ? B[j*ldb+k] : B[k*ldb+j].
+ * C is M x N with row pitch ldc.  Pitches are in elements.  M, N, K >= 0 (K = 0 writes +0). */
+int repdl_b200_mm(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K,
+                  int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc, void *stream);
+
+/* ---- convolution -----------------------------------------------------------------------
+ * Replace repdl::cuda::convolution::{conv2d, conv2d_grad_input, conv2d_grad_kernel}
+ * (backend/cuda/convolution.cu:153-173, 259-277, 359-377); bits defined by
+ * backend/cpu/convolution.cpp:12-52, 54-90, 92-128.  NCHW input, [OC][IC/groups][KH][KW]
+ * kernel, OH = (H + 2*pH - KH)/sH + 1.  Taps that fall in the padding are skipped, not
+ * multiplied by zero.  Only conv2d takes groups (as in the reference). */
+int repdl_b200_conv2d(const float *input, const float *kernel, float *output, int64_t N,
+                      int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH, int64_t KW,
+                      int64_t sH, int64_t sW, int64_t pH, int64_t pW, int64_t groups,
+                      void *stream);
+int repdl_b200_conv2d_grad_input(const float *grad_output, const float *kernel,
+                                 float *grad_input, int64_t N, int64_t IC, int64_t H, int64_t W,
+                                 int64_t OC, int64_t KH, int64_t KW, int64_t sH, int64_t sW,
+                                 int64_t pH, int64_t pW, void *stream);
+int repdl_b200_conv2d_grad_kernel(const float *grad_output, const float *input,
+                                  float *grad_kernel, int64_t N, int64_t IC, int64_t H,
+                                  int64_t W, int64_t OC, int64_t KH, int64_t KW, int64_t sH,
+                                  int64_t sW, int64_t pH, int64_t pW, void *stream);
+
+/* ---- fixed-order sums --------------------------------------------------------------------
+ * Replace repdl::cuda::summation::{sum1d, sum2d_dim0, sum2d_dim1, sum4d_dim023}
+ * (backend/cuda/summation.cu:33-43, 59-71, 94-105, 132-144); bits defined by
+ * backend/cpu/summation.cpp:12-78: every result is a strict left-to-right fp32 chain from
+ * +0, multiplied once by `factor` at the end (1.0f, or float(1.0/count) for a mean).
+ *
+ * sum1d reproduces one chain of n elements.  It needs scratch: pass a buffer of at least
+ * repdl_b200_sum1d_scratch_bytes(n) bytes, 256-byte aligned; its contents on entry do not
+ * matter and it may be reused by the next call on the same stream. */
+size_t repdl_b200_sum1d_scratch_bytes(int64_t n);
+int repdl_b200_sum1d(const float *x, float *out, int64_t n, float factor, void *scratch,
+                     size_t scratch_bytes, void *stream);
+/* out[j] = factor * chain over i of x[i*N + j]   (M rows, N columns) */
+int repdl_b200_sum2d_dim0(const float *x, float *out, int64_t M, int64_t N, float factor,
+                          void *stream);
+/* out[i] = factor * chain over j of x[i*N + j] */
+int repdl_b200_sum2d_dim1(const float *x, float *out, int64_t M, int64_t N, float factor,
+                          void *stream);
+/* out[c] = factor * chain over (n, h*w) of x[n][c][h][w];  HW = H*W */
+int repdl_b200_sum4d_dim023(const float *x, float *out, int64_t N, int64_t C, int64_t HW,
+                            float factor, void *stream);
+
+/* ---- elementwise math ----------------------------------------------------------------------
+ * exp / log replace repdl::cuda::math::{exp2d, log1d} (backend/cuda/math.cu:20-66); bits defined
+ * by backend/cpu/math.cpp:14-47: (float)exp((double)x), (float)log((double)x) with glibc's
+ * double-precision libm, i.e. exact -> nearest fp64 -> nearest fp32.
+ * div / sqrt replace what repdl/ops.py:98-103 and :122-123 compute through ATen: IEEE fp32
+ * division and correctly rounded square root, with the x86 NaN conventions of the reference's
+ * CPU run (NaN operands come back quieted with sign and payload kept; invalid operations give
+ * 0xFFC00000 for div and 0x7FC00000 for sqrt of a negative). */
+int repdl_b200_exp(const float *x, float *y, int64_t n, void *stream);
+int repdl_b200_log(const float *x, float *y, int64_t n, void *stream);
+int repdl_b200_sqrt(const float *x, float *y, int64_t n, void *stream);
+int repdl_b200_div_scalar(const float *x, float divisor, float *y, int64_t n, void *stream);
+int repdl_b200_div(const float *x, const float *divisor, float *y, int64_t n, void *stream);
+
+/* ---- composites ------------------------------------------------------------------------------
+ * Replace repdl::cuda::softmax::softmax (backend/cuda/softmax.cpp:15-21) and
+ * repdl::cuda::cross_entropy::cross_entropy (backend/cuda/cross_entropy.cpp:15-24); bits defined by
+ * backend/cpu/softmax.cpp:15-21 and backend/cpu/cross_entropy.cpp:15-24.  x is [M][N]; target holds
+ * M int64 class indices.  cross_entropy writes one float (the mean loss) to `loss` and needs
+ * M floats of scratch for the per-row terms. */
+int repdl_b200_softmax(const float *x, float *y, int64_t M, int64_t N, void *stream);
+int repdl_b200_cross_entropy(const float *x, const int64_t *target, float *loss, int64_t M,
+                             int64_t N, float *row_scratch, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* REPDL_B200_H */

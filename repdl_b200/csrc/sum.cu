@@ -1,0 +1,209 @@
+// Fixed-order fp32 sums for sm_100a.
+//
+// Contract (microsoft/RepDL backend/cpu/summation.cpp:12-78): each result is ONE fp32 accumulator
+// that starts at +0 and receives the elements strictly left to right with a rounded fp32 add after
+// every element; the mean variants multiply the finished sum once by float(1.0/count).  There is no
+// tree: the chain itself is the specification, so a sum is parallel only across independent chains
+// (rows, columns, channels).  No atomics anywhere.
+#include "common.cuh"
+
+namespace repdl_b200 {
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// sum2d_dim1: one chain per row.  One thread owns one row and walks it with 128-bit loads; the 32
+// rows of a warp are 32 separate 128-byte lines per step, each of which stays in L1 until its owner
+// has consumed all of it, so every DRAM sector is fetched once.  UNROLL independent loads are kept
+// in flight per thread (UNROLL * 16 B * resident threads covers the HBM latency-bandwidth product).
+// ------------------------------------------------------------------------------------------------
+template <int UNROLL>
+__global__ void __launch_bounds__(128)
+sum_rows_vec_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t M, int64_t N,
+                    float factor)
+{
+    int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= M) return;
+    const float4 *p = reinterpret_cast<const float4 *>(x + row * N);
+    const int64_t nv = N >> 2;
+    float s = 0.0f;
+    int64_t j = 0;
+    for (; j + UNROLL <= nv; j += UNROLL) {
+        float4 v[UNROLL];
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) v[u] = __ldg(p + j + u);
+#pragma unroll
+        for (int u = 0; u < UNROLL; u++) {
+            s = __fadd_rn(s, v[u].x);
+            s = __fadd_rn(s, v[u].y);
+            s = __fadd_rn(s, v[u].z);
+            s = __fadd_rn(s, v[u].w);
+        }
+    }
+    for (; j < nv; j++) {
+        float4 v = __ldg(p + j);
+        s = __fadd_rn(s, v.x);
+        s = __fadd_rn(s, v.y);
+        s = __fadd_rn(s, v.z);
+        s = __fadd_rn(s, v.w);
+    }
+    out[row] = __fmul_rn(factor, s);
+}
+
+__global__ void __launch_bounds__(128)
+sum_rows_scalar_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t M, int64_t N,
+                       float factor)
+{
+    int64_t row = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (row >= M) return;
+    const float *p = x + row * N;
+    float s = 0.0f;
+    for (int64_t j = 0; j < N; j++) s = __fadd_rn(s, __ldg(p + j));
+    out[row] = __fmul_rn(factor, s);
+}
+
+// ------------------------------------------------------------------------------------------------
+// sum2d_dim0: one chain per column; a warp reads 32 adjacent columns of one row per step, which is
+// already coalesced.  8 rows are loaded ahead of the adds.
+// ------------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(128)
+sum_cols_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t M, int64_t N,
+                float factor)
+{
+    int64_t col = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= N) return;
+    const float *p = x + col;
+    float s = 0.0f;
+    int64_t i = 0;
+    for (; i + 8 <= M; i += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; u++) v[u] = __ldg(p + (i + u) * N);
+#pragma unroll
+        for (int u = 0; u < 8; u++) s = __fadd_rn(s, v[u]);
+    }
+    for (; i < M; i++) s = __fadd_rn(s, __ldg(p + i * N));
+    out[col] = __fmul_rn(factor, s);
+}
+
+// ------------------------------------------------------------------------------------------------
+// One long chain per CTA (sum1d: a single CTA; sum4d_dim023: one CTA per channel).  The chain is
+// the concatenation of `nseg` contiguous segments of `seglen` floats, segment s starting at
+// base + s * segstride.  All threads stage the next TILE chain elements into shared memory while
+// thread 0 walks the current tile with LDS.128 + four dependent adds; the walk (4 cycles per
+// element, the latency of a dependent FADD) is the critical path.
+// ------------------------------------------------------------------------------------------------
+constexpr int CHAIN_TILE = 4096;
+constexpr int CHAIN_THREADS = 256;
+
+__global__ void __launch_bounds__(CHAIN_THREADS)
+chain_sum_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t nseg, int64_t seglen,
+                 int64_t segstride, int64_t chain_stride, float factor)
+{
+    __shared__ __align__(16) float buf[2][CHAIN_TILE];
+    const float *base = x + (int64_t)blockIdx.x * chain_stride;
+    const int64_t total = nseg * seglen;
+    const int64_t ntiles = (total + CHAIN_TILE - 1) / CHAIN_TILE;
+    const int t = threadIdx.x;
+
+    auto stage = [&](int64_t tile, float *dst) {
+        int64_t e0 = tile * CHAIN_TILE;
+#pragma unroll 4
+        for (int i = t; i < CHAIN_TILE; i += CHAIN_THREADS) {
+            int64_t e = e0 + i;
+            float v = 0.0f;
+            if (e < total) {
+                int64_t s = (nseg == 1) ? 0 : e / seglen;
+                int64_t o = e - s * seglen;
+                v = __ldg(base + s * segstride + o);
+            }
+            dst[i] = v;
+        }
+    };
+
+    float s = 0.0f;
+    if (ntiles > 0) stage(0, buf[0]);
+    __syncthreads();
+    for (int64_t tile = 0; tile < ntiles; tile++) {
+        const int cur = (int)(tile & 1);
+        if (tile + 1 < ntiles) stage(tile + 1, buf[cur ^ 1]);
+        if (t == 0) {
+            int64_t left = total - tile * CHAIN_TILE;
+            int cnt = left < CHAIN_TILE ? (int)left : CHAIN_TILE;
+            const float4 *b4 = reinterpret_cast<const float4 *>(buf[cur]);
+            int i = 0;
+            for (; i + 4 <= cnt; i += 4) {
+                float4 v = b4[i >> 2];
+                s = __fadd_rn(s, v.x);
+                s = __fadd_rn(s, v.y);
+                s = __fadd_rn(s, v.z);
+                s = __fadd_rn(s, v.w);
+            }
+            for (; i < cnt; i++) s = __fadd_rn(s, buf[cur][i]);
+        }
+        __syncthreads();
+    }
+    if (t == 0) out[blockIdx.x] = __fmul_rn(factor, s);
+}
+
+}  // namespace
+}  // namespace repdl_b200
+
+using namespace repdl_b200;
+
+extern "C" size_t repdl_b200_sum1d_scratch_bytes(int64_t n)
+{
+    (void)n;
+    return 256;
+}
+
+extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float factor, void *scratch,
+                                size_t scratch_bytes, void *stream)
+{
+    if (n < 0) return REPDL_E_SHAPE;
+    if (!out || (n > 0 && !x)) return REPDL_E_NULL;
+    (void)scratch;
+    (void)scratch_bytes;
+    chain_sum_kernel<<<1, CHAIN_THREADS, 0, (cudaStream_t)stream>>>(x, out, 1, n, 0, 0, factor);
+    return launch_status();
+}
+
+extern "C" int repdl_b200_sum2d_dim0(const float *x, float *out, int64_t M, int64_t N, float factor,
+                                     void *stream)
+{
+    if (M < 0 || N < 0) return REPDL_E_SHAPE;
+    if (N == 0) return REPDL_OK;
+    if (!out || (M > 0 && !x)) return REPDL_E_NULL;
+    int64_t blocks = (N + 127) / 128;
+    if (blocks > 0x7FFFFFFF) return REPDL_E_RANGE;
+    sum_cols_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(x, out, M, N, factor);
+    return launch_status();
+}
+
+extern "C" int repdl_b200_sum2d_dim1(const float *x, float *out, int64_t M, int64_t N, float factor,
+                                     void *stream)
+{
+    if (M < 0 || N < 0) return REPDL_E_SHAPE;
+    if (M == 0) return REPDL_OK;
+    if (!out || (N > 0 && !x)) return REPDL_E_NULL;
+    int64_t blocks = (M + 127) / 128;
+    if (blocks > 0x7FFFFFFF) return REPDL_E_RANGE;
+    if (N % 4 == 0 && aligned16(x))
+        sum_rows_vec_kernel<8><<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(x, out, M, N,
+                                                                                   factor);
+    else
+        sum_rows_scalar_kernel<<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(x, out, M, N,
+                                                                                    factor);
+    return launch_status();
+}
+
+extern "C" int repdl_b200_sum4d_dim023(const float *x, float *out, int64_t N, int64_t C, int64_t HW,
+                                       float factor, void *stream)
+{
+    if (N < 0 || C < 0 || HW < 0) return REPDL_E_SHAPE;
+    if (C == 0) return REPDL_OK;
+    if (!out || (N * HW > 0 && !x)) return REPDL_E_NULL;
+    if (C > 0x7FFFFFFF) return REPDL_E_RANGE;
+    chain_sum_kernel<<<(unsigned)C, CHAIN_THREADS, 0, (cudaStream_t)stream>>>(x, out, N, HW, C * HW,
+                                                                              HW, factor);
+    return launch_status();
+}

@@ -1,0 +1,212 @@
+"""Small, seeded parity cases shared by the golden-fixture generator, the oracle tests (CPU) and
+the CUDA parity tests (GPU).  Each case is (name, op, args-builder); inputs are rebuilt from the
+seed wherever the case runs, so the fixtures only need to hold output hashes.
+
+`run_case(impl, case)` evaluates a case on an implementation that exposes the operator names of
+microsoft/RepDL's repdl/ops.py (the oracle package, the reference backend adapter below, or
+repdl_b200.ops with tensors moved to the GPU).
+"""
+import hashlib
+
+import torch
+
+
+def sha(t):
+    """SHA-256 of the tensor's bytes -- the comparator of the reference (repdl/utils.py:10-13)."""
+    return hashlib.sha256(t.detach().cpu().contiguous().numpy().tobytes()).hexdigest()
+
+
+def _g(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def _randn(seed, *shape, scale=1.0):
+    return torch.randn(*shape, generator=_g(seed)) * scale
+
+
+SPECIAL_BITS = [
+    0x7F800001, 0xFFC12345, 0x7FA5A5A5, 0xFF800000, 0x7F800000, 0x00000000, 0x80000000, 0x00000001,
+    0x80000001, 0x807FFFFF, 0x007FFFFF, 0x00800000, 0xC2B00000, 0x42B00000, 0xBF800000, 0x3F800000,
+    0xFFFFFFFF, 0x7FFFFFFF, 0x41178FEB, 0xC16912CD, 0x42B17218, 0x42B17217, 0xC2CFF1B5, 0xC2CFF1B4,
+    0xC2AEAC50, 0xC2AEAC4F, 0x3F7FFFFF, 0x3F800001, 0x7F7FFFFF, 0xFF7FFFFF, 0x33800000, 0xB3800000,
+]
+
+
+def special_values(extra_random=1 << 16, seed=11):
+    bits = torch.tensor([b - (1 << 32) if b >= (1 << 31) else b for b in SPECIAL_BITS],
+                        dtype=torch.int32)
+    rnd = torch.randint(-2 ** 31, 2 ** 31, (extra_random,), generator=_g(seed), dtype=torch.int64)
+    return torch.cat([bits, rnd.to(torch.int32)]).view(torch.float32)
+
+
+def build_cases():
+    cases = []
+    # ---- mm: tails around the tile sizes, all four transposes --------------------------------
+    shapes = [(1, 1, 1), (7, 5, 3), (33, 65, 17), (64, 64, 16), (65, 63, 15), (128, 128, 32),
+              (129, 127, 33), (200, 72, 130), (256, 10, 128), (10, 128, 256), (300, 260, 47),
+              (4, 4, 0)]
+    for si, (M, N, K) in enumerate(shapes):
+        for ta in (False, True):
+            for tb in (False, True):
+                def mk(M=M, N=N, K=K, ta=ta, tb=tb, si=si):
+                    a = _randn(100 + si, *((K, M) if ta else (M, K)))
+                    b = _randn(200 + si, *((N, K) if tb else (K, N)))
+                    return (a, b, ta, tb)
+                cases.append(("mm_%dx%dx%d_%d%d" % (M, N, K, ta, tb), "mm", mk))
+
+    # tiny products that underflow to -0 and a K tail: the padded tail must not flip -0 to +0
+    def mk_negzero():
+        a = torch.full((5, 19), -1e-30)
+        b = torch.full((19, 6), 1e-30)
+        a[0, :] = 0.0
+        return (a, b, False, False)
+    cases.append(("mm_negzero_tail", "mm", mk_negzero))
+
+    def mk_strided():
+        a = _randn(301, 40, 100)[:, 10:58]       # row pitch 100, 48 columns
+        b = _randn(302, 48, 80)[:, ::2]          # inner stride 2 -> copied by the wrapper
+        return (a, b, False, False)
+    cases.append(("mm_strided", "mm", mk_strided))
+
+    # ---- conv -----------------------------------------------------------------------------------
+    conv_cfgs = [
+        # N, IC, H, W, OC, KH, KW, stride, padding, groups
+        (2, 3, 9, 10, 4, 3, 3, (1, 1), (0, 0), 1),
+        (2, 4, 9, 10, 6, 3, 3, (2, 1), (1, 2), 2),
+        (3, 2, 7, 7, 5, 3, 2, (2, 3), (2, 2), 1),
+        (1, 1, 28, 28, 32, 3, 3, (1, 1), (0, 0), 1),
+        (2, 32, 12, 12, 64, 3, 3, (1, 1), (1, 1), 1),
+        (2, 8, 6, 6, 8, 1, 1, (1, 1), (0, 0), 8),
+        (1, 3, 5, 5, 2, 5, 5, (1, 1), (2, 2), 1),
+    ]
+    for ci, (N, IC, H, W, OC, KH, KW, s, p, g) in enumerate(conv_cfgs):
+        def mk(N=N, IC=IC, H=H, W=W, OC=OC, KH=KH, KW=KW, s=s, p=p, g=g, ci=ci):
+            return (_randn(400 + ci, N, IC, H, W), _randn(500 + ci, OC, IC // g, KH, KW), s, p, g)
+        cases.append(("conv2d_%d" % ci, "conv2d", mk))
+        if g == 1:
+            OH, OW = (H + 2 * p[0] - KH) // s[0] + 1, (W + 2 * p[1] - KW) // s[1] + 1
+
+            def mk_gi(N=N, IC=IC, H=H, W=W, OC=OC, KH=KH, KW=KW, s=s, p=p, ci=ci, OH=OH, OW=OW):
+                return ((N, IC, H, W), _randn(500 + ci, OC, IC, KH, KW),
+                        _randn(600 + ci, N, OC, OH, OW), s, p)
+
+            def mk_gk(N=N, IC=IC, H=H, W=W, OC=OC, KH=KH, KW=KW, s=s, p=p, ci=ci, OH=OH, OW=OW):
+                return (_randn(400 + ci, N, IC, H, W), (OC, IC, KH, KW),
+                        _randn(600 + ci, N, OC, OH, OW), s, p)
+            cases.append(("conv2d_grad_input_%d" % ci, "conv2d_grad_input", mk_gi))
+            cases.append(("conv2d_grad_kernel_%d" % ci, "conv2d_grad_kernel", mk_gk))
+
+    # ---- sums -----------------------------------------------------------------------------------
+    for n in (0, 1, 5, 4095, 4096, 4097, 100000):
+        for avg in (False, True):
+            if n == 0 and avg:
+                continue
+            cases.append(("sum1d_%d_%d" % (n, avg), "sum1d",
+                          lambda n=n, avg=avg: (_randn(700, n, scale=100.0), avg)))
+    # massive cancellation and binade hovering
+    def mk_cancel():
+        x = _randn(701, 50000, scale=1e6)
+        x[::2] = -x[1::2] * (1 + 2 ** -20)
+        return (x, False)
+    cases.append(("sum1d_cancel", "sum1d", mk_cancel))
+
+    def mk_hover():
+        x = _randn(702, 60000, scale=3.0)
+        x[0] = 1048576.0
+        return (x, False)
+    cases.append(("sum1d_hover", "sum1d", mk_hover))
+    for (M, N) in [(1, 1), (37, 53), (256, 10), (256, 128), (130, 4096), (5, 4100), (1, 7), (9, 1)]:
+        for kd in (False, True):
+            for avg in (False, True):
+                cases.append(("sum2d_dim0_%dx%d_%d%d" % (M, N, kd, avg), "sum2d_dim0",
+                              lambda M=M, N=N, kd=kd, avg=avg: (_randn(710, M, N, scale=10.0), kd, avg)))
+                cases.append(("sum2d_dim1_%dx%d_%d%d" % (M, N, kd, avg), "sum2d_dim1",
+                              lambda M=M, N=N, kd=kd, avg=avg: (_randn(711, M, N, scale=10.0), kd, avg)))
+    for (N, C, H, W) in [(3, 5, 7, 2), (4, 64, 24, 24), (2, 1, 1, 1), (5, 3, 13, 11)]:
+        for kd in (False, True):
+            for avg in (False, True):
+                cases.append(("sum4d_%dx%dx%dx%d_%d%d" % (N, C, H, W, kd, avg), "sum4d_dim023",
+                              lambda N=N, C=C, H=H, W=W, kd=kd, avg=avg:
+                              (_randn(720, N, C, H, W, scale=10.0), kd, avg)))
+
+    # ---- elementwise ----------------------------------------------------------------------------
+    cases.append(("exp_special", "exp", lambda: (special_values(),)))
+    cases.append(("log_special", "log", lambda: (special_values(),)))
+    cases.append(("log_abs_special", "log", lambda: (special_values().abs(),)))
+    cases.append(("sqrt_special", "sqrt", lambda: (special_values(),)))
+    cases.append(("div10_special", "div", lambda: (special_values(), 10.0)))
+    cases.append(("div_tensor_special", "div",
+                  lambda: (special_values(), torch.roll(special_values(), 7))))
+    cases.append(("exp_range", "exp", lambda: (torch.linspace(-110, 95, 200003),)))
+    cases.append(("log_range", "log", lambda: (torch.logspace(-44, 38, 200003),)))
+    cases.append(("exp_unaligned", "exp", lambda: (torch.linspace(-20, 20, 1003)[1:],)))
+
+    # ---- composites -----------------------------------------------------------------------------
+    for (M, N) in [(256, 10), (1, 1), (37, 1000), (64, 3)]:
+        cases.append(("softmax_%dx%d" % (M, N), "softmax",
+                      lambda M=M, N=N: (_randn(800, M, N, scale=5.0),)))
+        if M == 1:
+            continue  # the reference itself raises for one row (squeeze() makes it 0-d before log1d)
+        cases.append(("cross_entropy_%dx%d" % (M, N), "cross_entropy",
+                      lambda M=M, N=N: (_randn(800, M, N, scale=5.0),
+                                        torch.randint(0, N, (M,), generator=_g(801)))))
+    return cases
+
+
+def run_case(impl, case, to_device=None):
+    name, op, mk = case
+    args = mk()
+    if to_device is not None:
+        args = tuple(a.to(to_device) if isinstance(a, torch.Tensor) else a for a in args)
+    return getattr(impl, op)(*args)
+
+
+class RefAdapter:
+    """Presents the reference's CPU backend (oracle.ref()) under the names of repdl/ops.py."""
+
+    def __init__(self, ref):
+        self.cpu, self.math = ref.cpu, ref.math
+
+    def mm(self, a, b, ta=False, tb=False):
+        return self.cpu.mm(a, b, ta, tb)
+
+    def conv2d(self, x, k, s, p, g):
+        return self.cpu.conv2d(x, k, s[0], s[1], p[0], p[1], g)
+
+    def conv2d_grad_input(self, shape, k, go, s, p):
+        return self.cpu.conv2d_grad_input(go, k, shape[2], shape[3], s[0], s[1], p[0], p[1])
+
+    def conv2d_grad_kernel(self, x, wshape, go, s, p):
+        return self.cpu.conv2d_grad_kernel(go, x, wshape[2], wshape[3], s[0], s[1], p[0], p[1])
+
+    def sum1d(self, x, avg=False):
+        return self.cpu.sum1d(x, avg)
+
+    def sum2d_dim0(self, x, kd=False, avg=False):
+        return self.cpu.sum2d_dim0(x, kd, avg)
+
+    def sum2d_dim1(self, x, kd=False, avg=False):
+        return self.cpu.sum2d_dim1(x, kd, avg)
+
+    def sum4d_dim023(self, x, kd=False, avg=False):
+        return self.cpu.sum4d_dim023(x, kd, avg)
+
+    def exp(self, x):
+        return self.math.exp2d(x.view(1, -1)).view(x.shape)
+
+    def log(self, x):
+        return self.math.log1d(x.reshape(-1)).view(x.shape)
+
+    def sqrt(self, x):  # repdl/ops.py:122-123
+        return x.to(dtype=torch.float64).sqrt().to(dtype=torch.float32)
+
+    def div(self, x, other):  # repdl/ops.py:98-103
+        if isinstance(other, torch.Tensor):
+            return x.div(other)
+        return x.div(torch.tensor(other, device=x.device))
+
+    def softmax(self, x):
+        return self.cpu.softmax(x)
+
+    def cross_entropy(self, x, t):
+        return self.cpu.cross_entropy(x, t)

@@ -1,0 +1,132 @@
+"""GPU: every operator of librepdl_b200.so against the CPU oracle and the reference's golden
+fixtures, bit for bit.  All calls go through the C ABI (repdl_b200.ops -> ctypes)."""
+import json
+import os
+
+import pytest
+import torch
+
+import oracle
+from cases import build_cases, run_case, sha
+
+pytestmark = pytest.mark.gpu
+GOLDEN = os.path.join(os.path.dirname(__file__), "golden")
+CASES = build_cases()
+
+
+def golden(name):
+    with open(os.path.join(GOLDEN, name)) as f:
+        return json.load(f)
+
+
+def bits_equal(a, b):
+    a, b = a.detach().cpu().contiguous(), b.detach().cpu().contiguous()
+    if a.shape != b.shape:
+        print("shape", a.shape, b.shape)
+        return False
+    ai, bi = a.view(torch.int32).reshape(-1), b.view(torch.int32).reshape(-1)
+    if torch.equal(ai, bi):
+        return True
+    bad = (ai != bi).nonzero().view(-1)
+    print("%d of %d elements differ; first:" % (bad.numel(), ai.numel()),
+          [(int(i), "%08x" % (ai[i].item() & 0xFFFFFFFF), "%08x" % (bi[i].item() & 0xFFFFFFFF))
+           for i in bad[:8]])
+    return False
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from repdl_b200 import ops as o
+    return o
+
+
+@pytest.mark.parametrize("case", CASES, ids=[c[0] for c in CASES])
+def test_small_case(ops, case):
+    got = run_case(ops, case, to_device="cuda")
+    want = run_case(oracle, case)
+    assert got.is_cuda
+    assert bits_equal(got, want), case[0]
+    g = golden("small_cases.json")[case[0]]
+    assert list(got.shape) == g["shape"] and sha(got) == g["sha256"]
+
+
+def test_unaligned_pointers(ops):
+    """Device pointers that are only 4-byte aligned take the scalar paths."""
+    g = torch.Generator().manual_seed(21)
+    x = (torch.rand(100003, generator=g) * 40 - 20)
+    xd = x.cuda()
+    for off in (1, 2, 3):
+        v, vd = x[off:off + 90001].contiguous(), xd[off:off + 90001]
+        assert vd.data_ptr() % 16 != 0
+        assert bits_equal(ops.exp(vd), oracle.exp(v))
+        assert bits_equal(ops.log(vd.abs()), oracle.log(v.abs()))
+        assert bits_equal(ops.sqrt(vd.abs()), oracle.sqrt(v.abs()))
+        assert bits_equal(ops.div(vd, 10.0), oracle.div(v, 10.0))
+    a = torch.randn(65 * 36 + 1, generator=g)
+    b = torch.randn(36 * 44 + 3, generator=g)
+    am, bm = a[1:].view(65, 36), b[3:].view(36, 44)
+    amd, bmd = a.cuda()[1:].view(65, 36), b.cuda()[3:].view(36, 44)
+    assert bits_equal(ops.mm(amd, bmd), oracle.mm(am.contiguous(), bm.contiguous()))
+    r = torch.randn(33 * 64 + 1, generator=g)
+    assert bits_equal(ops.sum2d_dim1(r.cuda()[1:].view(33, 64)), oracle.sum2d_dim1(r[1:].view(33, 64)))
+
+
+def test_results_do_not_depend_on_run(ops):
+    g = torch.Generator().manual_seed(22)
+    a, b = torch.randn(513, 300, generator=g).cuda(), torch.randn(300, 257, generator=g).cuda()
+    first = ops.mm(a, b)
+    for _ in range(3):
+        assert torch.equal(first, ops.mm(a, b))
+
+
+def test_config1_mm_1024(ops):
+    from repdl_b200 import workloads
+    a, b = workloads.mm_square(1024, 0)
+    got = ops.mm(a.cuda(), b.cuda())
+    assert bits_equal(got, oracle.mm(a, b))
+    path = os.path.join(GOLDEN, "configs.json")
+    if os.path.exists(path):
+        assert sha(got) == golden("configs.json")["c1_mm_1024"]["sha256"]
+    # all four layouts of the same product give the same bits
+    at, bt = a.t().contiguous().cuda(), b.t().contiguous().cuda()
+    assert torch.equal(got, ops.mm(at, b.cuda(), transA=True))
+    assert torch.equal(got, ops.mm(a.cuda(), bt, transB=True))
+    assert torch.equal(got, ops.mm(at, bt, transA=True, transB=True))
+
+
+def test_config2_first_chunks(ops):
+    """Config 2 on its first two 2^24-element chunks, against the oracle run live."""
+    from repdl_b200 import workloads
+    gold = golden("configs.json")["c2_crmath_2p28"]["chunks"] if os.path.exists(
+        os.path.join(GOLDEN, "configs.json")) else None
+    for ci, x in enumerate(workloads.crmath_chunks(1 << 25, 1)):
+        xd = x.cuda()
+        res = {"div10": ops.div(xd, 10.0), "sqrt_abs": ops.sqrt(xd.abs()),
+               "exp": ops.exp(xd.view(4096, 4096)).view(-1), "log_abs": ops.log(xd.abs())}
+        want = {"div10": oracle.div(x, 10.0), "sqrt_abs": oracle.sqrt(x.abs()),
+                "exp": oracle.exp(x), "log_abs": oracle.log(x.abs())}
+        for k in res:
+            assert bits_equal(res[k], want[k]), (ci, k)
+            if gold:
+                assert sha(res[k]) == gold[ci][k], (ci, k)
+
+
+def test_config3_pieces(ops):
+    """Config 3 recipe on one 2^24 chunk: the 1-D chain and 4096 row chains."""
+    from repdl_b200 import workloads
+    x = next(iter(workloads.sum_chunks(1 << 24, 2)))
+    xd = x.cuda()
+    assert bits_equal(ops.sum1d(xd), oracle.sum1d(x))
+    assert bits_equal(ops.sum1d(xd, average=True), oracle.sum1d(x, average=True))
+    assert bits_equal(ops.sum2d_dim1(xd.view(4096, 4096)), oracle.sum2d_dim1(x.view(4096, 4096)))
+    assert bits_equal(ops.sum2d_dim0(xd.view(4096, 4096)), oracle.sum2d_dim0(x.view(4096, 4096)))
+
+
+def test_mm_linearity_in_rows(ops):
+    """Size-independent property used at full size: any row block of C equals the product of the
+    same row block of A with B (rows are independent chains), so sharding by rows keeps the bits."""
+    g = torch.Generator().manual_seed(23)
+    a, b = (torch.rand(2048, 1024, generator=g) * 2 - 1).cuda(), (torch.rand(1024, 2048, generator=g) * 2 - 1).cuda()
+    full = ops.mm(a, b)
+    for lo, hi in [(0, 256), (256, 1024), (1024, 1029), (1029, 2048)]:
+        assert torch.equal(full[lo:hi], ops.mm(a[lo:hi], b))
