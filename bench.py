@@ -1,0 +1,378 @@
+#!/usr/bin/env python
+"""Benchmark of the reproducible operator backend.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference] [--workload W]
+
+Headline workload (default): the bit-exact fp32 product of two 16384 x 16384 matrices drawn
+U[-1,1) from seed 4, A partitioned by rows over the N GPUs and C all-gathered, so that every rank
+ends with the full product.  A "step" is one such product.  One JSON line is printed by rank 0.
+
+  value      whole-job GFLOP/s (2 M N K per step) with operands resident in HBM
+  e2e        the same with HOST operands: pinned A panel and B copied in, C panel copied out,
+             every step, inside the timed region
+  roofline   the GEMM kernel against the FP32 FMA-pipe peak measured on this GPU by a pure-FFMA
+             probe kernel (tensor cores are not used: their accumulation order is not bit-specified)
+  cpu_baseline  the reference's own CPU backend on a bounded sample of rows, timed on the host cores
+  extra      (N = 1 only) the HBM-bound kernels of the same backend: exp/log/div/sqrt over 2^28
+             elements and the fixed-order sums, each with its own roofline against measured HBM
+
+`--impl reference` times the reference's CPU backend alone (rank 0 only) on a bounded row sample.
+"""
+import argparse
+import hashlib
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+
+def env_int(name, default):
+    return int(os.environ.get(name, default))
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return float(p["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """Samples nvidia-smi clocks and throttle reasons of one GPU while the timed region runs."""
+
+    Q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index, self.rows, self.proc = index, [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.Q,
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, pw, reasons = [], [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 7:
+                continue
+            try:
+                sm.append(float(r[0])), mx.append(float(r[1])), pw.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[3:7]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        sm.sort()
+        return {"sm_mhz": sm[len(sm) // 2] if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "power_w_max": max(pw) if pw else None, "samples": len(sm),
+                "reasons": sorted(reasons)}
+
+
+def event_ms(fn, stream=None):
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    fn()
+    e1.record(stream)
+    e1.synchronize()
+    return e0.elapsed_time(e1)
+
+
+def ffma_peak_tflops(fp64=False):
+    """FP32 (or FP64) FMA-pipe peak of the current GPU from the library's probe kernel."""
+    import ctypes
+    from repdl_b200._cabi import check, lib
+    out = torch.zeros(4, dtype=torch.float64, device="cuda")
+    flops = ctypes.c_double(0)
+    iters = 1 << (14 if fp64 else 16)
+
+    def run():
+        check(lib.repdl_b200_probe_fma(int(fp64), iters, 8, out.data_ptr(), ctypes.byref(flops), None),
+              "probe")
+    run()
+    torch.cuda.synchronize()
+    best = min(event_ms(run) for _ in range(5))
+    return flops.value / best / 1e9
+
+
+def load_reference_cpu():
+    """The reference's CPU backend built into oracle/_ref (preferred), else the C oracle port."""
+    import oracle
+    ref = oracle.ref()
+    if ref is not None:
+        return "reference", ref.cpu.mm, torch.get_num_threads()
+    return "port", lambda a, b, ta, tb: oracle.mm(a, b, ta, tb), oracle.num_threads()
+
+
+def time_cpu_mm(a, b, budget_s, rows0=4):
+    """Times the CPU mm on the first rows of A; grows the sample until it fills the budget."""
+    kind, fn, cores = load_reference_cpu()
+    K, N = b.shape
+    rows = rows0
+    t = time.perf_counter()
+    fn(a[:rows].contiguous(), b, False, False)
+    dt = time.perf_counter() - t
+    want = int(max(rows, min(a.shape[0], rows * budget_s / max(dt, 1e-3))))
+    want = max(rows0, (want // rows0) * rows0)
+    if want > rows * 2:
+        rows = want
+        t = time.perf_counter()
+        fn(a[:rows].contiguous(), b, False, False)
+        dt = time.perf_counter() - t
+    gflops = 2.0 * rows * N * K / dt / 1e9
+    return {"value": gflops, "unit": "GFLOP/s", "cores": cores, "kind": kind,
+            "sample": "first %d of %d rows of A times the full B (%.1f s)" % (rows, a.shape[0], dt)}
+
+
+def run_reference(args, rank):
+    """--impl reference: the reference's own CPU implementation of the path, rank 0 only."""
+    if rank != 0:
+        return
+    from repdl_b200 import workloads
+    n = args.size
+    a, b = workloads.mm_large(n, 4)
+    kind, fn, cores = load_reference_cpu()
+    rows = args.ref_rows
+    sample = a[:rows].contiguous()
+    for _ in range(args.warmup):
+        fn(sample[:max(1, rows // 4)], b, False, False)
+    t = time.perf_counter()
+    for _ in range(args.steps):
+        fn(sample, b, False, False)
+    dt = time.perf_counter() - t
+    gflops = 2.0 * rows * n * n * args.steps / dt / 1e9
+    line = {
+        "impl": "reference", "metric": "bit-exact fp32 mm GFLOP/s", "value": gflops,
+        "unit": "GFLOP/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": dt / args.steps * 1e3, "higher_is_better": True, "scaling": "strong",
+        "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "mm M=N=K=%d (config 5), reference CPU backend on a row sample" % n,
+                   "sample_rows": rows},
+        "cpu_baseline": {"value": gflops, "unit": "GFLOP/s", "cores": cores, "kind": kind,
+                         "sample": "each step = first %d of %d rows of A times the full B" % (rows, n)},
+        "e2e": {"value": gflops, "unit": "GFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def extras_hbm(hbm_peak, peak_kind):
+    """N = 1: the HBM-bound kernels (configs 2 and 3) with their own rooflines."""
+    from repdl_b200 import ops, workloads
+    out = {}
+    gold_path = os.path.join(ROOT, "tests", "golden", "configs.json")
+    gold = json.load(open(gold_path)) if os.path.exists(gold_path) else None
+    n = 1 << 28
+    x = torch.cat(list(workloads.crmath_chunks(n, 1)))
+    xa = x.abs()  # on the CPU: torch's CUDA abs() would canonicalise NaN payloads
+    xd, xad = x.cuda(), xa.cuda()
+    del x, xa
+    for name, fn, key in (("div(x,10)", lambda: ops.div(xd, 10.0), "div10"),
+                          ("sqrt(|x|)", lambda: ops.sqrt(xad), "sqrt_abs"),
+                          ("exp(x)", lambda: ops.exp(xd), "exp"),
+                          ("log(|x|)", lambda: ops.log(xad), "log_abs")):
+        for _ in range(3):
+            y = fn()
+        torch.cuda.synchronize()
+        ms = min(event_ms(fn) for _ in range(5))
+        rec = {"ms": ms, "GB/s": 8.0 * n / ms / 1e6, "frac_of_%s_hbm" % peak_kind: 8.0 * n / ms / 1e6 / hbm_peak,
+               "elements": n}
+        if gold:
+            rec["sha256_equal_reference_cpu"] = (
+                hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
+                == gold["c2_crmath_2p28"]["whole"][key])
+        out[name] = rec
+        del y
+    del xd, xad
+    torch.cuda.empty_cache()
+    # sums: rows 65536 x 4096 (the first 2^28 elements of the config-3 stream)
+    r = torch.cat(list(workloads.sum_chunks(1 << 28, 2))).view(65536, 4096).cuda()
+    fn = lambda: ops.sum2d_dim1(r)  # noqa: E731
+    for _ in range(3):
+        y = fn()
+    torch.cuda.synchronize()
+    ms = min(event_ms(fn) for _ in range(5))
+    rec = {"ms": ms, "GB/s": 4.0 * r.numel() / ms / 1e6,
+           "frac_of_%s_hbm" % peak_kind: 4.0 * r.numel() / ms / 1e6 / hbm_peak}
+    if gold:
+        rec["sha256_equal_reference_cpu"] = (hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
+                                             == gold["c3_sum_rows_65536x4096"]["sha256"])
+    out["sum rows [65536,4096]"] = rec
+    return out
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=5)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--size", type=int, default=16384, help="M = N = K of the headline product")
+    ap.add_argument("--mode", default="auto", choices=["auto", "nccl", "p2p"])
+    ap.add_argument("--stripes", type=int, default=4)
+    ap.add_argument("--ref-rows", type=int, default=16)
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--no-extra", action="store_true")
+    ap.add_argument("--no-e2e", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = max(args.warmup, 0)
+
+    rank, world = env_int("RANK", 0), env_int("WORLD_SIZE", 1)
+    local_rank = env_int("LOCAL_RANK", 0)
+    if args.impl == "reference":
+        run_reference(args, rank)
+        return
+
+    import torch.distributed as dist
+    from repdl_b200 import workloads
+    from repdl_b200.dist import ShardedMM, mm_from_host
+
+    torch.cuda.set_device(local_rank)
+    dev = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=dev)
+
+    n = args.size
+    Mp = n // world
+    a, b = workloads.mm_large(n, 4)
+    a_host = a[rank * Mp:(rank + 1) * Mp].contiguous().pin_memory()
+    b_host = b.pin_memory()
+    a_dev, b_dev = a_host.to(dev), b_host.to(dev)
+    mode = "nccl" if args.mode == "auto" else args.mode
+    sh = ShardedMM(n, n, n, device=dev, mode=mode, stripes=args.stripes if world > 1 else 1)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(args.warmup):
+        sh(a_dev, b_dev)
+    barrier()
+    sampler = ClockSampler(local_rank)
+    if rank == 0:
+        sampler.start()
+    sh.kernel_launches = 0
+    kern_ev = []
+    cur = torch.cuda.current_stream()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(cur)
+    for _ in range(args.steps):
+        sh(a_dev, b_dev)
+    e1.record(cur)
+    barrier()
+    ms_total = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    launches = sh.kernel_launches
+
+    # kernel-only duration of this rank's GEMM launch (events on the launching stream)
+    kms = []
+    for _ in range(max(3, args.steps)):
+        kms.append(event_ms(lambda: sh._mm_into(a_dev, b_dev, sh.C[sh.row0:sh.row0 + Mp]), cur))
+    kernel_ms = sum(kms) / len(kms)
+
+    t = torch.tensor([ms_total, kernel_ms], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms_total, kernel_ms = float(t[0]), float(t[1])
+    ms_step = ms_total / args.steps
+    flops_step = 2.0 * n * n * n
+    value = flops_step / ms_step / 1e6  # GFLOP/s
+
+    # end to end with host operands
+    e2e = None
+    if not args.no_e2e:
+        c_host = torch.empty((Mp, n), dtype=torch.float32).pin_memory()
+        for _ in range(2):
+            mm_from_host(sh, a_host, b_host, a_dev, b_dev, c_host)
+        barrier()
+        ke = min(args.steps, 3)
+        t0 = torch.cuda.Event(enable_timing=True)
+        t1 = torch.cuda.Event(enable_timing=True)
+        t0.record(cur)
+        for _ in range(ke):
+            mm_from_host(sh, a_host, b_host, a_dev, b_dev, c_host)
+        t1.record(cur)
+        barrier()
+        t = torch.tensor([t0.elapsed_time(t1)], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_ms = float(t[0]) / ke
+        e2e = {"value": flops_step / e2e_ms / 1e6, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
+               "h2d_bytes_per_step": world * (a_host.numel() + b_host.numel()) * 4,
+               "d2h_bytes_per_step": world * c_host.numel() * 4}
+
+    # parity of the timed result against the golden hash of the reference CPU backend
+    parity = None
+    if rank == 0:
+        gpath = os.path.join(ROOT, "tests", "golden", "mm16k.json")
+        if n == 16384 and os.path.exists(gpath):
+            gold = json.load(open(gpath))
+            h = hashlib.sha256(sh.C.cpu().numpy().tobytes()).hexdigest()
+            parity = "sha256 equal to reference CPU backend" if h == gold["sha256"] else "MISMATCH"
+
+    if rank == 0:
+        hbm_peak, peak_kind = measured_peaks()
+        peak = ffma_peak_tflops(False)
+        achieved = flops_step / world / kernel_ms / 1e9  # TFLOP/s of one rank's launch
+        line = {
+            "metric": "bit-exact fp32 mm GFLOP/s", "value": value, "unit": "GFLOP/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms_step,
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32",
+            "data": "synthetic",
+            "config": {"workload": "mm M=N=K=%d fp32, A,B~U[-1,1) seed 4 (config 5); A row-sharded, "
+                                   "C all-gathered" % n,
+                       "parallelism": "rows/%d" % world, "collective": sh.mode,
+                       "stripes": sh.stripes, "l2": "operands (3 GiB) exceed the 126 MB L2"},
+            "roofline": {"bound": "fp32_ffma", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
+                         "frac": achieved / peak, "traffic": None,
+                         "peak_source": "FFMA-only probe kernel timed in this run",
+                         "peak_nominal": 148 * 128 * 2 * 1.965e9 / 1e12,
+                         "kernel_ms": kernel_ms},
+            "clocks": clocks, "e2e": e2e, "gpu_launches": launches * world, "parity": parity,
+        }
+        if world == 1:
+            line["cpu_baseline"] = time_cpu_mm(a, b, args.cpu_budget)
+            if not args.no_extra:
+                del a_dev, b_dev, sh
+                torch.cuda.empty_cache()
+                line["extra"] = extras_hbm(hbm_peak, peak_kind)
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

@@ -5,9 +5,22 @@ A from-scratch replacement for the CUDA operator backend of microsoft/RepDL
 `repdl_b200.ops` mirrors the reference's `repdl.ops` names and argument meaning;
 `repdl_b200.install()` registers the PyTorch extension as `repdl.backend.cuda` so the reference's
 own Python layers run on top of these kernels unchanged.
-"""
-from . import _cabi  # noqa: F401  (raises if the CUDA library is missing)
-from . import ops  # noqa: F401
-from .dropin import install  # noqa: F401
 
-__all__ = ["ops", "install"]
+Submodules load on first use (so that `python -m repdl_b200.build` can run before the shared
+library exists); touching `ops` without a built librepdl_b200.so raises ImportError -- there is no
+fallback implementation.
+"""
+import importlib
+
+__all__ = ["ops", "install", "workloads", "build"]
+
+
+def install():
+    from .dropin import install as _install
+    return _install()
+
+
+def __getattr__(name):
+    if name in ("ops", "workloads", "build", "_cabi", "dropin", "nn", "optim", "dist"):
+        return importlib.import_module("." + name, __name__)
+    raise AttributeError(name)

@@ -17,6 +17,10 @@ namespace repdl_b200 {
 
 constexpr int kNumSMsB200 = 148;
 
+// The CUDA runtime keeps one "last error" per host thread, shared with every other library in the
+// process (PyTorch included).  Each entry point drops whatever an earlier, unrelated call left
+// there, so that launch_status() reports only this library's own launches.
+static inline void clear_stale_error() { (void)cudaGetLastError(); }
 // Status of the launch that was just enqueued on this thread (0 or a cudaError_t).
 static inline int launch_status() { return (int)cudaGetLastError(); }
 
@@ -39,6 +43,36 @@ __device__ __forceinline__ float4 ldg_stream_f4(const float *p)
 __device__ __forceinline__ void stg_stream_f4(float *p, float4 v)
 {
     __stcs(reinterpret_cast<float4 *>(p), v);
+}
+
+// cp.async (LDGSTS): 16-byte global -> shared copy that bypasses registers.
+__device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src)
+{
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait()
+{
+    asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
+}
+
+// Opt in to more than 48 KB of dynamic shared memory, once per device, for one kernel.  `done_mask`
+// must be a static that belongs to that kernel alone (bit d set: applied on device d).
+template <class Kern>
+int ensure_smem(Kern kern, int bytes, unsigned long long *done_mask)
+{
+    if (bytes <= 48 * 1024) return 0;
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    unsigned long long bit = 1ull << (dev & 63);
+    if (__atomic_load_n(done_mask, __ATOMIC_ACQUIRE) & bit) return 0;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e != cudaSuccess) return (int)e;
+    __atomic_fetch_or(done_mask, bit, __ATOMIC_RELEASE);
+    return 0;
 }
 
 }  // namespace repdl_b200

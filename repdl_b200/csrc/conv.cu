@@ -161,6 +161,7 @@ extern "C" int repdl_b200_conv2d(const float *input, const float *kernel, float 
                                  int64_t KW, int64_t sH, int64_t sW, int64_t pH, int64_t pW,
                                  int64_t groups, void *stream)
 {
+    clear_stale_error();
     ConvDims d;
     int e = fill_dims(d, N, IC, H, W, OC, KH, KW, sH, sW, pH, pW, groups);
     if (e) return e;
@@ -180,6 +181,7 @@ extern "C" int repdl_b200_conv2d_grad_input(const float *grad_output, const floa
                                             int64_t sH, int64_t sW, int64_t pH, int64_t pW,
                                             void *stream)
 {
+    clear_stale_error();
     ConvDims d;
     int e = fill_dims(d, N, IC, H, W, OC, KH, KW, sH, sW, pH, pW, 1);
     if (e) return e;
@@ -199,6 +201,7 @@ extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const flo
                                              int64_t sH, int64_t sW, int64_t pH, int64_t pW,
                                              void *stream)
 {
+    clear_stale_error();
     ConvDims d;
     int e = fill_dims(d, N, IC, H, W, OC, KH, KW, sH, sW, pH, pW, 1);
     if (e) return e;

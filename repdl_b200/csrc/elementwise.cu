@@ -9,19 +9,83 @@
 namespace repdl_b200 {
 namespace {
 
+// exp/log read one table entry per element at a data-dependent index; the tables (256 B and
+// 1.5 KB) are staged in shared memory once per CTA so that those reads never leave the SM.
+struct SmemTables {
+    const double *p;  // [0,32) 2^(j/32); [32,96) c_i; [96,160) -log c_i hi; [160,224) lo
+    __device__ __forceinline__ double exp_t(int j) const { return p[j]; }
+    __device__ __forceinline__ double log_c(int i) const { return p[32 + i]; }
+    __device__ __forceinline__ double log_t_hi(int i) const { return p[96 + i]; }
+    __device__ __forceinline__ double log_t_lo(int i) const { return p[160 + i]; }
+};
+constexpr int TABLE_DOUBLES = 224;
+
+__device__ __forceinline__ void stage_tables(double *sm)
+{
+    for (int i = threadIdx.x; i < TABLE_DOUBLES; i += blockDim.x) {
+        unsigned long long b = i < 32 ? CRM_EXP_T_HI[i]
+                             : i < 96 ? CRM_LOG_C[i - 32]
+                             : i < 160 ? CRM_LOG_T_HI[i - 96] : CRM_LOG_T_LO[i - 160];
+        sm[i] = __longlong_as_double((long long)b);
+    }
+    __syncthreads();
+}
+
+// An Op gives fast(x, tab, slow): the result of the branch-free path plus a flag "this element
+// needs slow(x)".  The kernels evaluate four elements, OR the flags and branch once.
 struct OpSqrt {
-    __device__ __forceinline__ float operator()(float x) const { return cr_sqrt(x); }
+    static constexpr bool kTables = false;
+    __device__ __forceinline__ float fast(float x, SmemTables, bool &slow) const
+    {
+        slow = false;
+        return cr_sqrt(x);
+    }
+    __device__ __forceinline__ float slow(float x) const { return cr_sqrt(x); }
 };
 struct OpExp {
-    __device__ __forceinline__ float operator()(float x) const { return cr_exp(x); }
+    static constexpr bool kTables = true;
+    __device__ __forceinline__ float fast(float x, SmemTables t, bool &slow) const
+    {
+        return cr_exp_fast(x, t, slow);
+    }
+    __device__ __forceinline__ float slow(float x) const { return crm_exp_slow(x); }
 };
 struct OpLog {
-    __device__ __forceinline__ float operator()(float x) const { return cr_log(x); }
+    static constexpr bool kTables = true;
+    __device__ __forceinline__ float fast(float x, SmemTables t, bool &slow) const
+    {
+        return cr_log_fast(x, t, slow);
+    }
+    __device__ __forceinline__ float slow(float x) const { return crm_log_slow(x); }
 };
 struct OpDivScalar {
+    static constexpr bool kTables = false;
     float d;
-    __device__ __forceinline__ float operator()(float x) const { return cr_div(x, d); }
+    __device__ __forceinline__ float fast(float x, SmemTables, bool &slow) const
+    {
+        slow = false;
+        return cr_div(x, d);
+    }
+    __device__ __forceinline__ float slow(float x) const { return cr_div(x, d); }
 };
+
+template <class Op>
+__device__ __forceinline__ float4 apply4(const Op &op, float4 v, SmemTables tab)
+{
+    bool s0, s1, s2, s3;
+    float4 r;
+    r.x = op.fast(v.x, tab, s0);
+    r.y = op.fast(v.y, tab, s1);
+    r.z = op.fast(v.z, tab, s2);
+    r.w = op.fast(v.w, tab, s3);
+    if (s0 | s1 | s2 | s3) {  // rare
+        if (s0) r.x = op.slow(v.x);
+        if (s1) r.y = op.slow(v.y);
+        if (s2) r.z = op.slow(v.z);
+        if (s3) r.w = op.slow(v.w);
+    }
+    return r;
+}
 
 constexpr int EW_THREADS = 256;
 constexpr int EW_VEC_PER_THREAD = 4;  // float4 groups in flight per thread per iteration
@@ -31,6 +95,9 @@ __global__ void __launch_bounds__(EW_THREADS)
 unary_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t nvec, Op op)
 {
     // nvec = number of float4 groups; x and y are 16-byte aligned
+    __shared__ double tables[Op::kTables ? TABLE_DOUBLES : 1];
+    if (Op::kTables) stage_tables(tables);
+    const SmemTables tab{tables};
     const int64_t stride = (int64_t)gridDim.x * EW_THREADS * EW_VEC_PER_THREAD;
     for (int64_t base = (int64_t)blockIdx.x * EW_THREADS * EW_VEC_PER_THREAD + threadIdx.x;
          base < nvec; base += stride) {
@@ -44,12 +111,7 @@ unary_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t nve
         for (int u = 0; u < EW_VEC_PER_THREAD; u++) {
             int64_t i = base + (int64_t)u * EW_THREADS;
             if (i < nvec) {
-                float4 r;
-                r.x = op(v[u].x);
-                r.y = op(v[u].y);
-                r.z = op(v[u].z);
-                r.w = op(v[u].w);
-                stg_stream_f4(y + 4 * i, r);
+                stg_stream_f4(y + 4 * i, apply4(op, v[u], tab));
             }
         }
     }
@@ -59,9 +121,18 @@ template <class Op>
 __global__ void __launch_bounds__(EW_THREADS)
 unary_scalar_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t n, Op op)
 {
+    __shared__ double tables[Op::kTables ? TABLE_DOUBLES : 1];
+    if (Op::kTables) stage_tables(tables);
+    const SmemTables tab{tables};
     const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
     for (int64_t i = (int64_t)blockIdx.x * EW_THREADS + threadIdx.x; i < n; i += stride)
-        y[i] = op(__ldg(x + i));
+    {
+        bool slow;
+        const float v = __ldg(x + i);
+        float r = op.fast(v, tab, slow);
+        if (slow) r = op.slow(v);
+        y[i] = r;
+    }
 }
 
 __global__ void __launch_bounds__(EW_THREADS)
@@ -115,28 +186,33 @@ using namespace repdl_b200;
 
 extern "C" int repdl_b200_exp(const float *x, float *y, int64_t n, void *stream)
 {
+    clear_stale_error();
     return launch_unary(x, y, n, OpExp{}, stream);
 }
 
 extern "C" int repdl_b200_log(const float *x, float *y, int64_t n, void *stream)
 {
+    clear_stale_error();
     return launch_unary(x, y, n, OpLog{}, stream);
 }
 
 extern "C" int repdl_b200_sqrt(const float *x, float *y, int64_t n, void *stream)
 {
+    clear_stale_error();
     return launch_unary(x, y, n, OpSqrt{}, stream);
 }
 
 extern "C" int repdl_b200_div_scalar(const float *x, float divisor, float *y, int64_t n,
                                      void *stream)
 {
+    clear_stale_error();
     return launch_unary(x, y, n, OpDivScalar{divisor}, stream);
 }
 
 extern "C" int repdl_b200_div(const float *x, const float *divisor, float *y, int64_t n,
                               void *stream)
 {
+    clear_stale_error();
     if (n < 0) return REPDL_E_SHAPE;
     if (n == 0) return REPDL_OK;
     if (!x || !y || !divisor) return REPDL_E_NULL;

@@ -71,6 +71,7 @@ using namespace repdl_b200;
 
 extern "C" int repdl_b200_softmax(const float *x, float *y, int64_t M, int64_t N, void *stream)
 {
+    clear_stale_error();
     if (M < 0 || N < 0) return REPDL_E_SHAPE;
     if (M == 0 || N == 0) return REPDL_OK;
     if (!x || !y) return REPDL_E_NULL;
@@ -83,6 +84,7 @@ extern "C" int repdl_b200_softmax(const float *x, float *y, int64_t M, int64_t N
 extern "C" int repdl_b200_cross_entropy(const float *x, const int64_t *target, float *loss,
                                         int64_t M, int64_t N, float *row_scratch, void *stream)
 {
+    clear_stale_error();
     if (M <= 0 || N <= 0) return REPDL_E_SHAPE;
     if (!x || !target || !loss) return REPDL_E_NULL;
     if (!row_scratch) return REPDL_E_SCRATCH;

@@ -15,22 +15,36 @@
 // inner loop).  The slab that holds the K tail is padded with A = -0.0f, B = +0.0f: the padded
 // product is -0, and acc + (-0) == acc for EVERY acc including -0, +0, inf and NaN, so the padded
 // steps are exact identities (a +0 pad would turn an accumulator of -0 into +0).
+//
+// The inner product runs on Blackwell's packed FP32 FMA, fma.rn.f32x2: one instruction performs two
+// independent IEEE single-rounding FMAs on a 64-bit register pair -- the same bits as two scalar
+// FFMAs, in half the issue slots, which leaves room for the shared-memory loads without starving
+// the FMA pipe.  Accumulators live as (j, j+1) column pairs; the B fragment arrives as pairs from
+// LDS.128; the A slab is stored in shared memory with every value DUPLICATED, so that the (a, a)
+// broadcast pair also arrives straight from LDS.128 with no register moves.
 #include "common.cuh"
 
 namespace repdl_b200 {
 namespace {
 
-constexpr int BK = 16;
+#ifndef REPDL_MM_BK
+#define REPDL_MM_BK 16
+#endif
+#ifndef REPDL_MM_MINB_BIG
+#define REPDL_MM_MINB_BIG 1
+#endif
+constexpr int BK = REPDL_MM_BK;
 
 // Cooperative loader for one operand slab of BX (rows or columns of C) x BK (k).
 //   KCONTIG = true : element (x, k) lives at X[x * ld + k]   (A of a plain mm, B of transB)
 //   KCONTIG = false: element (x, k) lives at X[k * ld + x]   (B of a plain mm, A of transA)
 //   VEC            : 128-bit global loads (caller guarantees 16 B alignment of every group)
-// Shared layout is always S[k][x] with row pitch BX + 4.
-template <int BX, int NT, bool KCONTIG, bool VEC>
+//   DUP            : every value is written twice, S[k][2x] = S[k][2x+1] (the A operand)
+// Shared layout is always S[k][x] (S[k][2x], S[k][2x+1] when DUP) with a padded row pitch.
+template <int BX, int NT, bool KCONTIG, bool VEC, bool DUP>
 struct SlabLoader {
     static constexpr int NV = BX * BK / 4 / NT;
-    static constexpr int PITCH = BX + 4;
+    static constexpr int PITCH = (DUP ? 2 * BX : BX) + 4;
     float4 v[NV];
 
     __device__ __forceinline__ void load(const float *__restrict__ X, int64_t ld, int x0, int k0,
@@ -77,14 +91,28 @@ struct SlabLoader {
             if (KCONTIG) {
                 int x = idx / (BK / 4);
                 int k = (idx % (BK / 4)) * 4;
-                S[k + 0][x] = v[i].x;
-                S[k + 1][x] = v[i].y;
-                S[k + 2][x] = v[i].z;
-                S[k + 3][x] = v[i].w;
+                if (DUP) {
+                    *reinterpret_cast<float2 *>(&S[k + 0][2 * x]) = make_float2(v[i].x, v[i].x);
+                    *reinterpret_cast<float2 *>(&S[k + 1][2 * x]) = make_float2(v[i].y, v[i].y);
+                    *reinterpret_cast<float2 *>(&S[k + 2][2 * x]) = make_float2(v[i].z, v[i].z);
+                    *reinterpret_cast<float2 *>(&S[k + 3][2 * x]) = make_float2(v[i].w, v[i].w);
+                } else {
+                    S[k + 0][x] = v[i].x;
+                    S[k + 1][x] = v[i].y;
+                    S[k + 2][x] = v[i].z;
+                    S[k + 3][x] = v[i].w;
+                }
             } else {
                 int k = idx / (BX / 4);
                 int x = (idx % (BX / 4)) * 4;
-                *reinterpret_cast<float4 *>(&S[k][x]) = v[i];
+                if (DUP) {
+                    *reinterpret_cast<float4 *>(&S[k][2 * x]) =
+                        make_float4(v[i].x, v[i].x, v[i].y, v[i].y);
+                    *reinterpret_cast<float4 *>(&S[k][2 * x + 4]) =
+                        make_float4(v[i].z, v[i].z, v[i].w, v[i].w);
+                } else {
+                    *reinterpret_cast<float4 *>(&S[k][x]) = v[i];
+                }
             }
         }
     }
@@ -104,18 +132,33 @@ __device__ __forceinline__ void tile_of_cta(int pid, int tilesM, int tilesN, int
     tn = r / gsz;
 }
 
-template <int BM, int BN, bool A_KC, bool B_KC, bool VEC, int MINB>
-__global__ void __launch_bounds__((BM / 8) * (BN / 8), MINB)
+// Thread tile TM x TN (multiples of 4): TM/4 row quads and TN/4 column quads, quad q of a thread
+// sitting q * (tile extent / quads) apart, so that the 8 lanes of a warp that differ in their
+// column read 8 consecutive 16-byte groups of a shared-memory row (no bank conflicts) and lanes that
+// share a row or a column get their fragment by broadcast.
+#ifndef REPDL_MM_F2
+#define REPDL_MM_F2 0   // 1: inner product on the packed fma.rn.f32x2 (same bits; measured slower)
+#endif
+#ifndef REPDL_MM_ORDER
+#define REPDL_MM_ORDER 0
+#endif
+constexpr bool kF2 = REPDL_MM_F2 != 0;
+
+template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB>
+__global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB)
 sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C,
              int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int tilesM, int tilesN,
              int vecC)
 {
-    constexpr int NT = (BM / 8) * (BN / 8);
-    constexpr int WX = BN / 64;  // warps along n (a warp spans 8 threads = 32 + 32 columns)
-    using LoadA = SlabLoader<BM, NT, A_KC, VEC>;
-    using LoadB = SlabLoader<BN, NT, B_KC, VEC>;
-    __shared__ __align__(16) float As[2][BK][LoadA::PITCH];
-    __shared__ __align__(16) float Bs[2][BK][LoadB::PITCH];
+    constexpr int NT = (BM / TM) * (BN / TN);
+    constexpr int QM = TM / 4, QN = TN / 4;
+    constexpr int WX = (BN / TN) / 8;  // warps along n; a warp is 8 lanes along n x 4 along m
+    using LoadA = SlabLoader<BM, NT, A_KC, VEC, kF2>;
+    using LoadB = SlabLoader<BN, NT, B_KC, VEC, false>;
+    constexpr int PA = LoadA::PITCH, PB = LoadB::PITCH;
+    extern __shared__ __align__(16) float smem[];
+    float(*As)[BK][PA] = reinterpret_cast<float(*)[BK][PA]>(smem);
+    float(*Bs)[BK][PB] = reinterpret_cast<float(*)[BK][PB]>(smem + 2 * BK * PA);
 
     int tm, tn;
     tile_of_cta(blockIdx.x, tilesM, tilesN, tm, tn);
@@ -124,14 +167,16 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     const int lane = t & 31, wid = t >> 5;
     const int tx = (wid % WX) * 8 + (lane & 7);
     const int ty = (wid / WX) * 4 + (lane >> 3);
-    const int c0 = tx * 4, c1 = BN / 2 + tx * 4;
-    const int r0 = ty * 4, r1 = BM / 2 + ty * 4;
 
-    float acc[8][8];
+    float acc[TM][TN];                   // scalar mode
+    unsigned long long acc2[TM][TN / 2];  // packed mode: columns (2p, 2p+1) of row i
 #pragma unroll
-    for (int i = 0; i < 8; i++)
+    for (int i = 0; i < TM; i++) {
 #pragma unroll
-        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+        for (int j = 0; j < TN; j++) acc[i][j] = 0.0f;
+#pragma unroll
+        for (int j = 0; j < TN / 2; j++) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
+    }
 
     LoadA la;
     LoadB lb;
@@ -151,16 +196,50 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
         }
 #pragma unroll
         for (int k = 0; k < BK; k++) {
-            float4 a0 = *reinterpret_cast<const float4 *>(&As[cur][k][r0]);
-            float4 a1 = *reinterpret_cast<const float4 *>(&As[cur][k][r1]);
-            float4 b0 = *reinterpret_cast<const float4 *>(&Bs[cur][k][c0]);
-            float4 b1 = *reinterpret_cast<const float4 *>(&Bs[cur][k][c1]);
-            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
-            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+            if constexpr (kF2) {
+                unsigned long long a[TM], b[TN / 2];  // a[i] = (a_i, a_i); b[p] = (b_2p, b_2p+1)
 #pragma unroll
-            for (int i = 0; i < 8; i++)
+                for (int q = 0; q < QM; q++) {
+                    const float *src = &As[cur][k][2 * (q * (BM / QM) + ty * 4)];
+                    ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(src);
+                    ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(src + 4);
+                    a[q * 4 + 0] = v0.x, a[q * 4 + 1] = v0.y, a[q * 4 + 2] = v1.x, a[q * 4 + 3] = v1.y;
+                }
 #pragma unroll
-                for (int j = 0; j < 8; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+                for (int q = 0; q < QN; q++) {
+                    ulonglong2 v =
+                        *reinterpret_cast<const ulonglong2 *>(&Bs[cur][k][q * (BN / QN) + tx * 4]);
+                    b[q * 2 + 0] = v.x, b[q * 2 + 1] = v.y;
+                }
+#pragma unroll
+                for (int i = 0; i < TM; i++)
+#pragma unroll
+                    for (int j = 0; j < TN / 2; j++)
+                        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[i][j]) : "l"(a[i]), "l"(b[j]));
+            } else {
+                float a[TM], b[TN];
+#pragma unroll
+                for (int q = 0; q < QM; q++) {
+                    float4 v = *reinterpret_cast<const float4 *>(&As[cur][k][q * (BM / QM) + ty * 4]);
+                    a[q * 4 + 0] = v.x, a[q * 4 + 1] = v.y, a[q * 4 + 2] = v.z, a[q * 4 + 3] = v.w;
+                }
+#pragma unroll
+                for (int q = 0; q < QN; q++) {
+                    float4 v = *reinterpret_cast<const float4 *>(&Bs[cur][k][q * (BN / QN) + tx * 4]);
+                    b[q * 4 + 0] = v.x, b[q * 4 + 1] = v.y, b[q * 4 + 2] = v.z, b[q * 4 + 3] = v.w;
+                }
+#if REPDL_MM_ORDER == 0
+#pragma unroll
+                for (int i = 0; i < TM; i++)
+#pragma unroll
+                    for (int j = 0; j < TN; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+#else
+#pragma unroll
+                for (int j = 0; j < TN; j++)
+#pragma unroll
+                    for (int i = 0; i < TM; i++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+#endif
+            }
         }
         if (more) {
             la.store(As[cur ^ 1], t);
@@ -170,39 +249,57 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     }
 
 #pragma unroll
-    for (int i = 0; i < 8; i++) {
-        int row = m0 + (i < 4 ? r0 + i : r1 + i - 4);
+    for (int i = 0; i < TM; i++) {
+        int row = m0 + (i / 4) * (BM / QM) + ty * 4 + (i % 4);
         if (row >= M) continue;
         float *crow = C + (int64_t)row * ldc;
 #pragma unroll
-        for (int h = 0; h < 2; h++) {
-            int col = n0 + (h ? c1 : c0);
+        for (int q = 0; q < QN; q++) {
+            int col = n0 + q * (BN / QN) + tx * 4;
+            float c[4];
+            if constexpr (kF2) {
+                asm("mov.b64 {%0,%1}, %2;" : "=f"(c[0]), "=f"(c[1]) : "l"(acc2[i][q * 2 + 0]));
+                asm("mov.b64 {%0,%1}, %2;" : "=f"(c[2]), "=f"(c[3]) : "l"(acc2[i][q * 2 + 1]));
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) c[j] = acc[i][q * 4 + j];
+            }
             if (vecC) {
                 if (col < N)
-                    *reinterpret_cast<float4 *>(crow + col) =
-                        make_float4(acc[i][h * 4 + 0], acc[i][h * 4 + 1], acc[i][h * 4 + 2],
-                                    acc[i][h * 4 + 3]);
+                    *reinterpret_cast<float4 *>(crow + col) = make_float4(c[0], c[1], c[2], c[3]);
             } else {
 #pragma unroll
                 for (int j = 0; j < 4; j++)
-                    if (col + j < N) crow[col + j] = acc[i][h * 4 + j];
+                    if (col + j < N) crow[col + j] = c[j];
             }
         }
     }
 }
 
-template <int BM, int BN, bool A_KC, bool B_KC, bool VEC, int MINB>
+template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB>
 int launch_one(const float *A, const float *B, float *C, int M, int N, int K, int64_t lda,
                int64_t ldb, int64_t ldc, int vecC, cudaStream_t st)
 {
     int tilesM = (M + BM - 1) / BM, tilesN = (N + BN - 1) / BN;
     int64_t tiles = (int64_t)tilesM * tilesN;
     if (tiles > 0x7FFFFFFF) return REPDL_E_RANGE;
-    sgemm_kernel<BM, BN, A_KC, B_KC, VEC, MINB>
-        <<<(unsigned)tiles, (BM / 8) * (BN / 8), 0, st>>>(A, B, C, M, N, K, lda, ldb, ldc, tilesM,
-                                                           tilesN, vecC);
+    auto kern = sgemm_kernel<BM, BN, TM, TN, A_KC, B_KC, VEC, MINB>;
+    constexpr int smem_bytes = 2 * BK * ((kF2 ? 2 : 1) * BM + 4 + BN + 4) * (int)sizeof(float);
+    static unsigned long long smem_done = 0;  // one mask per kernel instantiation
+    int e = ensure_smem(kern, smem_bytes, &smem_done);
+    if (e) return e;
+    kern<<<(unsigned)tiles, (BM / TM) * (BN / TN), smem_bytes, st>>>(A, B, C, M, N, K, lda, ldb, ldc,
+                                                                      tilesM, tilesN, vecC);
     return launch_status();
 }
+
+#ifndef REPDL_MM_BM
+#define REPDL_MM_BM 128
+#define REPDL_MM_BN 256
+#define REPDL_MM_TM 8
+#define REPDL_MM_TN 16
+#endif
+#define REPDL_MM_BIG REPDL_MM_BM, REPDL_MM_BN, REPDL_MM_TM, REPDL_MM_TN
 
 template <bool A_KC, bool B_KC, bool VEC>
 int launch_shape(const float *A, const float *B, float *C, int M, int N, int K, int64_t lda,
@@ -210,13 +307,15 @@ int launch_shape(const float *A, const float *B, float *C, int M, int N, int K, 
 {
     // Big tiles once they fill the machine twice over; small tiles otherwise so that a
     // 1024 x 1024 problem still spreads over all 148 SMs.
-    int64_t big = (int64_t)((M + 127) / 128) * ((N + 127) / 128);
+    int64_t big = (int64_t)((M + REPDL_MM_BM - 1) / REPDL_MM_BM) * ((N + REPDL_MM_BN - 1) / REPDL_MM_BN);
     if (big >= 2 * (int64_t)sm_count())
-        return launch_one<128, 128, A_KC, B_KC, VEC, 2>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
+        return launch_one<REPDL_MM_BIG, A_KC, B_KC, VEC, REPDL_MM_MINB_BIG>(A, B, C, M, N, K, lda,
+                                                                           ldb, ldc, vecC, st);
     int64_t mid = (int64_t)((M + 127) / 128) * ((N + 63) / 64);
     if (mid >= 2 * (int64_t)sm_count())
-        return launch_one<128, 64, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
-    return launch_one<64, 64, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
+        return launch_one<128, 64, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC,
+                                                             st);
+    return launch_one<64, 64, 8, 8, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
 }
 
 }  // namespace
@@ -243,6 +342,7 @@ extern "C" int repdl_b200_mm(const float *A, const float *B, float *C, int64_t M
                              int64_t K, int transA, int transB, int64_t lda, int64_t ldb,
                              int64_t ldc, void *stream)
 {
+    clear_stale_error();
     if (M < 0 || N < 0 || K < 0) return REPDL_E_SHAPE;
     if (M == 0 || N == 0) return REPDL_OK;
     if (!C || (K > 0 && (!A || !B))) return REPDL_E_NULL;

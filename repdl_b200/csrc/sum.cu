@@ -49,6 +49,77 @@ sum_rows_vec_kernel(const float *__restrict__ x, float *__restrict__ out, int64_
     out[row] = __fmul_rn(factor, s);
 }
 
+// Staged variant (the fast path): a warp owns 32 rows.  Per stage it copies a [32 rows x 64 columns]
+// block to shared memory with cp.async -- 16 lanes cover 256 contiguous bytes of one row, so DRAM
+// sees whole 128-byte lines -- three stages deep, and each lane then walks its own row of the
+// block with LDS.128 (row pitch 68 floats: the 8 lanes of a quarter-warp hit 8 different 16-byte
+// bank groups).  Warps never synchronise with each other.
+constexpr int SR_COLS = 64, SR_PITCH = 68, SR_STAGES = 3, SR_WARPS = 2;
+constexpr int SR_SMEM_BYTES = SR_WARPS * SR_STAGES * 32 * SR_PITCH * (int)sizeof(float);
+
+__global__ void __launch_bounds__(SR_WARPS * 32)
+sum_rows_staged_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t M, int64_t N,
+                       float factor)
+{
+    extern __shared__ __align__(16) float sr_smem[];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int64_t row0 = ((int64_t)blockIdx.x * SR_WARPS + warp) * 32;
+    if (row0 >= M) return;
+    float(*buf)[32][SR_PITCH] =
+        reinterpret_cast<float(*)[32][SR_PITCH]>(sr_smem + warp * SR_STAGES * 32 * SR_PITCH);
+    const int64_t nst = (N + SR_COLS - 1) / SR_COLS;
+    const int sub = lane >> 4, c = (lane & 15) * 4;
+
+    auto issue = [&](int64_t st) {
+        if (st < nst) {
+            const int64_t col = st * SR_COLS + c;
+            if (col < N) {
+                float(*dst)[SR_PITCH] = buf[st % SR_STAGES];
+#pragma unroll
+                for (int i = 0; i < 16; i++) {
+                    int r = i * 2 + sub;
+                    int64_t grow = row0 + r;
+                    if (grow >= M) grow = M - 1;  // duplicate the last row; its sum is discarded
+                    cp_async_16(&dst[r][c], x + grow * N + col);
+                }
+            }
+        }
+        cp_async_commit();
+    };
+
+#pragma unroll
+    for (int s = 0; s < SR_STAGES - 1; s++) issue(s);
+    float acc = 0.0f;
+    for (int64_t st = 0; st < nst; st++) {
+        issue(st + SR_STAGES - 1);
+        cp_async_wait<SR_STAGES - 1>();
+        __syncwarp();
+        const int64_t left = N - st * SR_COLS;
+        const int cnt = left < SR_COLS ? (int)left : SR_COLS;  // multiple of 4
+        const float4 *rowp = reinterpret_cast<const float4 *>(buf[st % SR_STAGES][lane]);
+        if (cnt == SR_COLS) {
+#pragma unroll
+            for (int q = 0; q < SR_COLS / 4; q++) {
+                float4 v = rowp[q];
+                acc = __fadd_rn(acc, v.x);
+                acc = __fadd_rn(acc, v.y);
+                acc = __fadd_rn(acc, v.z);
+                acc = __fadd_rn(acc, v.w);
+            }
+        } else {
+            for (int q = 0; q < cnt / 4; q++) {
+                float4 v = rowp[q];
+                acc = __fadd_rn(acc, v.x);
+                acc = __fadd_rn(acc, v.y);
+                acc = __fadd_rn(acc, v.z);
+                acc = __fadd_rn(acc, v.w);
+            }
+        }
+        __syncwarp();
+    }
+    if (row0 + lane < M) out[row0 + lane] = __fmul_rn(factor, acc);
+}
+
 __global__ void __launch_bounds__(128)
 sum_rows_scalar_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t M, int64_t N,
                        float factor)
@@ -159,6 +230,7 @@ extern "C" size_t repdl_b200_sum1d_scratch_bytes(int64_t n)
 extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float factor, void *scratch,
                                 size_t scratch_bytes, void *stream)
 {
+    clear_stale_error();
     if (n < 0) return REPDL_E_SHAPE;
     if (!out || (n > 0 && !x)) return REPDL_E_NULL;
     (void)scratch;
@@ -170,6 +242,7 @@ extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float fac
 extern "C" int repdl_b200_sum2d_dim0(const float *x, float *out, int64_t M, int64_t N, float factor,
                                      void *stream)
 {
+    clear_stale_error();
     if (M < 0 || N < 0) return REPDL_E_SHAPE;
     if (N == 0) return REPDL_OK;
     if (!out || (M > 0 && !x)) return REPDL_E_NULL;
@@ -182,12 +255,20 @@ extern "C" int repdl_b200_sum2d_dim0(const float *x, float *out, int64_t M, int6
 extern "C" int repdl_b200_sum2d_dim1(const float *x, float *out, int64_t M, int64_t N, float factor,
                                      void *stream)
 {
+    clear_stale_error();
     if (M < 0 || N < 0) return REPDL_E_SHAPE;
     if (M == 0) return REPDL_OK;
     if (!out || (N > 0 && !x)) return REPDL_E_NULL;
     int64_t blocks = (M + 127) / 128;
     if (blocks > 0x7FFFFFFF) return REPDL_E_RANGE;
-    if (N % 4 == 0 && aligned16(x))
+    if (N % 4 == 0 && aligned16(x) && N >= 2 * SR_COLS) {
+        static unsigned long long smem_done = 0;
+        int e = ensure_smem(sum_rows_staged_kernel, SR_SMEM_BYTES, &smem_done);
+        if (e) return e;
+        int64_t b2 = (M + SR_WARPS * 32 - 1) / (SR_WARPS * 32);
+        sum_rows_staged_kernel<<<(unsigned)b2, SR_WARPS * 32, SR_SMEM_BYTES, (cudaStream_t)stream>>>(
+            x, out, M, N, factor);
+    } else if (N % 4 == 0 && aligned16(x))
         sum_rows_vec_kernel<8><<<(unsigned)blocks, 128, 0, (cudaStream_t)stream>>>(x, out, M, N,
                                                                                    factor);
     else
@@ -199,6 +280,7 @@ extern "C" int repdl_b200_sum2d_dim1(const float *x, float *out, int64_t M, int6
 extern "C" int repdl_b200_sum4d_dim023(const float *x, float *out, int64_t N, int64_t C, int64_t HW,
                                        float factor, void *stream)
 {
+    clear_stale_error();
     if (N < 0 || C < 0 || HW < 0) return REPDL_E_SHAPE;
     if (C == 0) return REPDL_OK;
     if (!out || (N * HW > 0 && !x)) return REPDL_E_NULL;

@@ -1,0 +1,154 @@
+"""Reproducible layers on top of repdl_b200.ops.
+
+Host-side mirror of the part of microsoft/RepDL's `repdl.nn` that the operator backend serves:
+Linear (repdl/nn/linear.py:11-54), Conv2d (repdl/nn/conv.py:11-115), CrossEntropyLoss
+(repdl/nn/loss.py:11-70) and `from_torch_module` (repdl/__init__.py:15-65).  Each autograd
+function calls the same operators in the same order as the reference's, so a model converted with
+this module and one converted with the reference's package produce identical bits.  Everything
+that is not a repdl operator (ReLU, max-pooling, flatten, bias adds, one-hot) is a single IEEE
+operation per element in torch and is left to torch, exactly as the reference does.
+"""
+from copy import copy
+
+import torch
+
+from . import ops
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        ctx.save_for_backward(x, weight)
+        out = ops.mm(x, weight, transB=True)       # x [B,in] times weight[out,in]^T
+        if bias is not None:
+            out += bias
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        x, weight = ctx.saved_tensors
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.mm(g, weight)
+        if ctx.needs_input_grad[1]:
+            gw = ops.mm(g, x, transA=True)
+        if ctx.needs_input_grad[2]:
+            gb = ops.sum2d_dim0(g)
+        return gx, gw, gb
+
+
+def linear(x, weight, bias=None):
+    if x.dim() != 2:
+        raise NotImplementedError("linear expects a 2-d input")
+    return _Linear.apply(x, weight, bias)
+
+
+class Linear(torch.nn.Linear):
+    def forward(self, x):
+        return linear(x, self.weight, self.bias)
+
+
+class _Conv2d(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, weight, bias, stride, padding, groups):
+        ctx.save_for_backward(x, weight)
+        ctx.cfg = (stride, padding, groups)
+        out = ops.conv2d(x, weight, stride, padding, groups)
+        if bias is not None:
+            out += bias.unsqueeze(-1).unsqueeze(-1)
+        return out
+
+    @staticmethod
+    def backward(ctx, g):
+        stride, padding, groups = ctx.cfg
+        if groups != 1:
+            raise NotImplementedError("grouped convolution has no backward (as in the reference)")
+        x, weight = ctx.saved_tensors
+        gx = gw = gb = None
+        if ctx.needs_input_grad[0]:
+            gx = ops.conv2d_grad_input(x.shape, weight, g, stride, padding)
+        if ctx.needs_input_grad[1]:
+            gw = ops.conv2d_grad_kernel(x, weight.shape, g, stride, padding)
+        if ctx.needs_input_grad[2]:
+            gb = ops.sum4d_dim023(g)
+        return gx, gw, gb, None, None, None
+
+
+def _pair(v):
+    return (v, v) if isinstance(v, int) else tuple(v)
+
+
+def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+    if isinstance(padding, str) or _pair(dilation) != (1, 1) or x.dim() != 4:
+        raise NotImplementedError("conv2d: string padding, dilation and non-4-d inputs are unsupported")
+    return _Conv2d.apply(x, weight, bias, _pair(stride), _pair(padding), groups)
+
+
+class Conv2d(torch.nn.Conv2d):
+    def forward(self, x):
+        if self.padding_mode != "zeros":
+            raise NotImplementedError("padding_mode must be 'zeros'")
+        return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+
+
+class _CrossEntropy(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, logits, target):
+        ctx.save_for_backward(logits, target)
+        return ops.cross_entropy(logits, target)
+
+    @staticmethod
+    def backward(ctx, g):
+        logits, target = ctx.saved_tensors
+        gl = None
+        if ctx.needs_input_grad[0]:
+            # (softmax - one_hot) * (1/B) * g : three separately rounded steps (repdl/nn/loss.py:29-33)
+            gl = ops.softmax(logits) - torch.nn.functional.one_hot(target, logits.shape[1])
+            gl *= 1.0 / logits.shape[0]
+            gl *= g
+        return gl, None
+
+
+def cross_entropy(logits, target):
+    if logits.dim() != 2 or target.dim() != 1:
+        raise NotImplementedError("cross_entropy expects [B, C] logits and [B] class indices")
+    return _CrossEntropy.apply(logits, target)
+
+
+class CrossEntropyLoss(torch.nn.CrossEntropyLoss):
+    def forward(self, logits, target):
+        if (self.weight is not None or self.ignore_index != -100 or self.reduction != "mean"
+                or self.label_smoothing != 0.0):
+            raise NotImplementedError("only the plain mean-reduced cross entropy is implemented")
+        return cross_entropy(logits, target)
+
+
+_SWAPS = {torch.nn.Linear: Linear, torch.nn.Conv2d: Conv2d, torch.nn.CrossEntropyLoss: CrossEntropyLoss}
+
+
+def from_torch_module(module):
+    """Returns a copy of `module` in which every torch.nn.Linear / Conv2d / CrossEntropyLoss (exact
+    types only) is replaced by its reproducible twin sharing the same parameter values; Sequential
+    containers are rebuilt and any other module is shallow-copied with converted children."""
+    cls = _SWAPS.get(type(module))
+    if cls is Linear:
+        new = Linear(module.in_features, module.out_features, module.bias is not None,
+                     device=module.weight.device, dtype=module.weight.dtype)
+        new.load_state_dict(module.state_dict())
+        return new
+    if cls is Conv2d:
+        new = Conv2d(module.in_channels, module.out_channels, module.kernel_size, module.stride,
+                     module.padding, module.dilation, module.groups, module.bias is not None,
+                     module.padding_mode, device=module.weight.device, dtype=module.weight.dtype)
+        new.load_state_dict(module.state_dict())
+        return new
+    if cls is CrossEntropyLoss:
+        return CrossEntropyLoss(weight=module.weight, ignore_index=module.ignore_index,
+                                reduction=module.reduction, label_smoothing=module.label_smoothing)
+    if type(module) is torch.nn.Sequential:
+        return torch.nn.Sequential(*[from_torch_module(m) for m in module])
+    new = copy(module)
+    new._modules = dict(new._modules)
+    for name, child in module.named_children():
+        new._modules[name] = from_torch_module(child)
+    return new
