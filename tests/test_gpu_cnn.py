@@ -1,0 +1,114 @@
+"""GPU: configuration 4 -- the CNN training step (conv, ReLU, conv, ReLU, max-pool, flatten, linear,
+ReLU, linear, cross entropy; SGD lr 0.01; batch 256; the same batch every step) -- must reproduce,
+step by step, the hashes the reference's own Python layers produced on its CPU backend
+(tests/golden/cnn_steps.json, written by tests/golden/make_golden.py cnn)."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+GOLD = os.path.join(ROOT, "tests", "golden", "cnn_steps.json")
+
+
+def _hash_params(model):
+    import hashlib
+    h = hashlib.sha256()
+    for p in model.parameters():
+        h.update(p.data.cpu().numpy().tobytes())
+    return h.hexdigest()
+
+
+def _train(model, loss_fn, x, y, steps, checkpoints):
+    from cases import sha
+    seen = {}
+    for step in range(steps):
+        for p in model.parameters():
+            p.grad = None
+        logits = model(x)
+        loss = loss_fn(logits, y)
+        loss.backward()
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(p.grad.mul(-0.01))
+        if step in checkpoints:
+            seen[step] = {"loss_hex": "%08x" % (loss.detach().cpu().view(torch.int32).item() & 0xFFFFFFFF),
+                          "logits": sha(logits), "params": _hash_params(model)}
+    return seen
+
+
+@pytest.mark.skipif(not os.path.exists(GOLD), reason="cnn_steps.json not generated")
+def test_cnn_training_matches_reference_cpu_hashes():
+    from cases import sha
+    from repdl_b200 import nn as rnn
+    from repdl_b200 import workloads
+    gold = json.load(open(GOLD))
+    torch.manual_seed(3)
+    model = rnn.from_torch_module(workloads.cnn_torch_model())
+    x, y = workloads.cnn_batch(256)
+    assert [sha(x), sha(y)] == gold["input_sha256"]
+    assert _hash_params(model) == gold["init_params"]
+    model = model.cuda()
+    loss_fn = rnn.CrossEntropyLoss()
+    want = {s["step"]: s for s in gold["steps"]}
+    seen = _train(model, loss_fn, x.cuda(), y.cuda(), 100, set(want))
+    for step in sorted(want):
+        for key in ("loss_hex", "logits", "params"):
+            assert seen[step][key] == want[step][key], (step, key)
+    with torch.no_grad():
+        assert sha(model(x.cuda())) == gold["final_logits"]
+    assert _hash_params(model) == gold["final_params"]
+
+
+DROPIN = r"""
+import json, sys, torch
+sys.path.insert(0, {root!r})
+import repdl_b200
+ext = repdl_b200.install()                    # becomes repdl.backend.cuda
+sys.path.insert(0, {site!r})
+import repdl                                  # the reference's own, unmodified Python package
+assert repdl.ops.cuda is ext
+from repdl_b200 import workloads
+sys.path.insert(0, {tests!r})
+from cases import sha
+torch.manual_seed(3)
+model = repdl.from_torch_module(workloads.cnn_torch_model())
+x, y = workloads.cnn_batch(256)
+model = model.cuda(); x = x.cuda(); y = y.cuda()
+loss_fn = repdl.nn.CrossEntropyLoss()
+out = []
+for step in range(3):
+    for p in model.parameters():
+        p.grad = None
+    logits = model(x); loss = loss_fn(logits, y); loss.backward()
+    with torch.no_grad():
+        for p in model.parameters():
+            p.add_(p.grad.mul(-0.01))
+    out.append(dict(step=step, logits=sha(logits), params=repdl.utils.get_hash(model)))
+# the reference's Adam on top of these kernels runs too (repdl/optim.py)
+opt = repdl.optim.Adam(model.parameters(), lr=0.01)
+loss = loss_fn(model(x), y); opt.zero_grad(); loss.backward(); opt.step()
+print(json.dumps(out))
+"""
+
+
+@pytest.mark.skipif(not os.path.exists(GOLD), reason="cnn_steps.json not generated")
+def test_reference_python_layers_run_unchanged_on_the_dropin():
+    """`repdl.from_torch_module`, `repdl.nn` and `repdl.optim` of the reference run unmodified with
+    this package's extension installed as `repdl.backend.cuda`, and give the reference's hashes."""
+    import oracle
+    site = oracle.ref_site()
+    if site is None:
+        pytest.skip("the reference's Python package is not installed under oracle/_ref")
+    code = DROPIN.format(root=ROOT, site=site, tests=os.path.join(ROOT, "tests"))
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    got = json.loads(res.stdout.strip().splitlines()[-1])
+    want = {s["step"]: s for s in json.load(open(GOLD))["steps"]}
+    for rec in got:
+        assert rec["logits"] == want[rec["step"]]["logits"], rec["step"]
+        assert rec["params"] == want[rec["step"]]["params"], rec["step"]
