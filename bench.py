@@ -238,7 +238,6 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--size", type=int, default=16384, help="M = N = K of the headline product")
     ap.add_argument("--mode", default="auto", choices=["auto", "nccl", "p2p"])
-    ap.add_argument("--stripes", type=int, default=4)
     ap.add_argument("--ref-rows", type=int, default=16)
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--no-extra", action="store_true")
@@ -269,8 +268,7 @@ def main():
     a_host = a[rank * Mp:(rank + 1) * Mp].contiguous().pin_memory()
     b_host = b.pin_memory()
     a_dev, b_dev = a_host.to(dev), b_host.to(dev)
-    mode = "nccl" if args.mode == "auto" else args.mode
-    sh = ShardedMM(n, n, n, device=dev, mode=mode, stripes=args.stripes if world > 1 else 1)
+    sh = ShardedMM(n, n, n, device=dev, mode=args.mode)
 
     def barrier():
         if world > 1:
@@ -297,10 +295,14 @@ def main():
     launches = sh.kernel_launches
 
     # kernel-only duration of this rank's GEMM launch (events on the launching stream)
+    # (the local-panel kernel alone; in p2p mode the timed steps run the same kernel with the
+    # peer stores added to its epilogue)
+    scratch_rows = torch.empty((Mp, n), dtype=torch.float32, device=dev) if world > 1 else sh.my_rows()
     kms = []
     for _ in range(max(3, args.steps)):
-        kms.append(event_ms(lambda: sh._mm_into(a_dev, b_dev, sh.C[sh.row0:sh.row0 + Mp]), cur))
+        kms.append(event_ms(lambda: sh.mm_into(a_dev, b_dev, scratch_rows), cur))
     kernel_ms = sum(kms) / len(kms)
+    del scratch_rows
 
     t = torch.tensor([ms_total, kernel_ms], dtype=torch.float64, device=dev)
     if world > 1:
@@ -354,7 +356,7 @@ def main():
             "config": {"workload": "mm M=N=K=%d fp32, A,B~U[-1,1) seed 4 (config 5); A row-sharded, "
                                    "C all-gathered" % n,
                        "parallelism": "rows/%d" % world, "collective": sh.mode,
-                       "stripes": sh.stripes, "l2": "operands (3 GiB) exceed the 126 MB L2"},
+                       "l2": "operands (3 GiB) exceed the 126 MB L2"},
             "roofline": {"bound": "fp32_ffma", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak, "traffic": None,
                          "peak_source": "FFMA-only probe kernel timed in this run",

@@ -50,6 +50,17 @@ const char *repdl_b200_strerror(int status);
 int repdl_b200_mm(const float *A, const float *B, float *C, int64_t M, int64_t N, int64_t K,
                   int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc, void *stream);
 
+/* Row-sharded product for the GPUs of one node (no counterpart in the reference, which has no
+ * multi-GPU code): this rank holds rows [row0, row0 + M_local) of op(A) in A_rows and all of B;
+ * the kernel computes those rows of C exactly as repdl_b200_mm would and stores every finished
+ * tile into the same rows of ALL nranks C buffers (C_of_rank: HOST array of nranks device pointers,
+ * each the base of a full C with pitch ldc; peers' buffers must be mapped into this process, e.g.
+ * symmetric memory).  When every rank has run its call and the ranks have synchronised, each holds
+ * the full C.  No reduction is split across ranks, so the bits equal a single-GPU run. nranks <= 8. */
+int repdl_b200_mm_allgather(const float *A_rows, const float *B, float *const *C_of_rank, int nranks,
+                            int64_t row0, int64_t M_local, int64_t N, int64_t K, int transA,
+                            int transB, int64_t lda, int64_t ldb, int64_t ldc, void *stream);
+
 /* ---- convolution -----------------------------------------------------------------------
  * Replace repdl::cuda::convolution::{conv2d, conv2d_grad_input, conv2d_grad_kernel}
  * (backend/cuda/convolution.cu:153-173, 259-277, 359-377); bits defined by

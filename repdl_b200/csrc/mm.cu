@@ -132,6 +132,15 @@ __device__ __forceinline__ void tile_of_cta(int pid, int tilesM, int tilesN, int
     tn = r / gsz;
 }
 
+// Where a finished C tile goes: to one matrix, or -- for the row-sharded multi-GPU product -- to the
+// same rows of the C buffers of all ranks of the node (peer pointers over NVLink), so that the
+// all-gather happens tile by tile inside the GEMM epilogue instead of as a separate collective.
+constexpr int kMaxRanks = 8;
+struct OutSet {
+    float *p[kMaxRanks];
+    int n;
+};
+
 // Thread tile TM x TN (multiples of 4): TM/4 row quads and TN/4 column quads, quad q of a thread
 // sitting q * (tile extent / quads) apart, so that the 8 lanes of a warp that differ in their
 // column read 8 consecutive 16-byte groups of a shared-memory row (no bank conflicts) and lanes that
@@ -146,9 +155,8 @@ constexpr bool kF2 = REPDL_MM_F2 != 0;
 
 template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB)
-sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__restrict__ C,
-             int M, int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int tilesM, int tilesN,
-             int vecC)
+sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const OutSet out, int M,
+             int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int tilesM, int tilesN, int vecC)
 {
     constexpr int NT = (BM / TM) * (BN / TN);
     constexpr int QM = TM / 4, QN = TN / 4;
@@ -252,7 +260,6 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
     for (int i = 0; i < TM; i++) {
         int row = m0 + (i / 4) * (BM / QM) + ty * 4 + (i % 4);
         if (row >= M) continue;
-        float *crow = C + (int64_t)row * ldc;
 #pragma unroll
         for (int q = 0; q < QN; q++) {
             int col = n0 + q * (BN / QN) + tx * 4;
@@ -264,20 +271,23 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, float *__
 #pragma unroll
                 for (int j = 0; j < 4; j++) c[j] = acc[i][q * 4 + j];
             }
-            if (vecC) {
-                if (col < N)
-                    *reinterpret_cast<float4 *>(crow + col) = make_float4(c[0], c[1], c[2], c[3]);
-            } else {
+            for (int r = 0; r < out.n; r++) {
+                float *crow = out.p[r] + (int64_t)row * ldc;
+                if (vecC) {
+                    if (col < N)
+                        *reinterpret_cast<float4 *>(crow + col) = make_float4(c[0], c[1], c[2], c[3]);
+                } else {
 #pragma unroll
-                for (int j = 0; j < 4; j++)
-                    if (col + j < N) crow[col + j] = c[j];
+                    for (int j = 0; j < 4; j++)
+                        if (col + j < N) crow[col + j] = c[j];
+                }
             }
         }
     }
 }
 
 template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB>
-int launch_one(const float *A, const float *B, float *C, int M, int N, int K, int64_t lda,
+int launch_one(const float *A, const float *B, const OutSet &C, int M, int N, int K, int64_t lda,
                int64_t ldb, int64_t ldc, int vecC, cudaStream_t st)
 {
     int tilesM = (M + BM - 1) / BM, tilesN = (N + BN - 1) / BN;
@@ -302,7 +312,7 @@ int launch_one(const float *A, const float *B, float *C, int M, int N, int K, in
 #define REPDL_MM_BIG REPDL_MM_BM, REPDL_MM_BN, REPDL_MM_TM, REPDL_MM_TN
 
 template <bool A_KC, bool B_KC, bool VEC>
-int launch_shape(const float *A, const float *B, float *C, int M, int N, int K, int64_t lda,
+int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, int K, int64_t lda,
                  int64_t ldb, int64_t ldc, int vecC, cudaStream_t st)
 {
     // Big tiles once they fill the machine twice over; small tiles otherwise so that a
@@ -338,14 +348,15 @@ int sm_count()
 
 using namespace repdl_b200;
 
-extern "C" int repdl_b200_mm(const float *A, const float *B, float *C, int64_t M, int64_t N,
-                             int64_t K, int transA, int transB, int64_t lda, int64_t ldb,
-                             int64_t ldc, void *stream)
+static int mm_dispatch(const float *A, const float *B, const OutSet &out, int64_t M, int64_t N,
+                       int64_t K, int transA, int transB, int64_t lda, int64_t ldb, int64_t ldc,
+                       void *stream)
 {
-    clear_stale_error();
     if (M < 0 || N < 0 || K < 0) return REPDL_E_SHAPE;
     if (M == 0 || N == 0) return REPDL_OK;
-    if (!C || (K > 0 && (!A || !B))) return REPDL_E_NULL;
+    for (int r = 0; r < out.n; r++)
+        if (!out.p[r]) return REPDL_E_NULL;
+    if (K > 0 && (!A || !B)) return REPDL_E_NULL;
     if (M > 0x7FFFFFF0 || N > 0x7FFFFFF0 || K > 0x7FFFFFF0) return REPDL_E_RANGE;
     const bool a_kc = !transA, b_kc = transB != 0;
     // smallest legal pitches
@@ -356,14 +367,43 @@ extern "C" int repdl_b200_mm(const float *A, const float *B, float *C, int64_t M
     const bool vecA = aligned16(A) && lda % 4 == 0 && (a_kc ? K : M) % 4 == 0;
     const bool vecB = aligned16(B) && ldb % 4 == 0 && (b_kc ? K : N) % 4 == 0;
     const bool vec = vecA && vecB;
-    const int vecC = aligned16(C) && ldc % 4 == 0 && N % 4 == 0;
+    int vecC = ldc % 4 == 0 && N % 4 == 0;
+    for (int r = 0; r < out.n; r++) vecC = vecC && aligned16(out.p[r]);
     const int m = (int)M, n = (int)N, k = (int)K;
 #define REPDL_MM_CASE(AKC, BKC)                                                              \
-    (vec ? launch_shape<AKC, BKC, true>(A, B, C, m, n, k, lda, ldb, ldc, vecC, st)           \
-         : launch_shape<AKC, BKC, false>(A, B, C, m, n, k, lda, ldb, ldc, vecC, st))
+    (vec ? launch_shape<AKC, BKC, true>(A, B, out, m, n, k, lda, ldb, ldc, vecC, st)         \
+         : launch_shape<AKC, BKC, false>(A, B, out, m, n, k, lda, ldb, ldc, vecC, st))
     if (a_kc && !b_kc) return REPDL_MM_CASE(true, false);
     if (a_kc && b_kc) return REPDL_MM_CASE(true, true);
     if (!a_kc && !b_kc) return REPDL_MM_CASE(false, false);
     return REPDL_MM_CASE(false, true);
 #undef REPDL_MM_CASE
+}
+
+extern "C" int repdl_b200_mm(const float *A, const float *B, float *C, int64_t M, int64_t N,
+                             int64_t K, int transA, int transB, int64_t lda, int64_t ldb,
+                             int64_t ldc, void *stream)
+{
+    clear_stale_error();
+    OutSet out{};
+    out.p[0] = C;
+    out.n = 1;
+    return mm_dispatch(A, B, out, M, N, K, transA, transB, lda, ldb, ldc, stream);
+}
+
+extern "C" int repdl_b200_mm_allgather(const float *A_rows, const float *B, float *const *C_of_rank,
+                                       int nranks, int64_t row0, int64_t M_local, int64_t N,
+                                       int64_t K, int transA, int transB, int64_t lda, int64_t ldb,
+                                       int64_t ldc, void *stream)
+{
+    clear_stale_error();
+    if (nranks < 1 || nranks > kMaxRanks || row0 < 0) return REPDL_E_SHAPE;
+    if (!C_of_rank) return REPDL_E_NULL;
+    OutSet out{};
+    out.n = nranks;
+    for (int r = 0; r < nranks; r++) {
+        if (!C_of_rank[r]) return REPDL_E_NULL;
+        out.p[r] = C_of_rank[r] + row0 * ldc;
+    }
+    return mm_dispatch(A_rows, B, out, M_local, N, K, transA, transB, lda, ldb, ldc, stream);
 }

@@ -3,76 +3,107 @@
 microsoft/RepDL has no multi-GPU code; this is the one distributed strategy the operator backend
 needs: A is partitioned by rows, B is replicated, every rank computes its own row panel of C with
 the single-GPU kernel (no reduction is ever split, so the bits are those of a one-GPU run), and
-the panels are all-gathered so that every rank ends with the full C.
+the panels are gathered so that every rank ends with the full C.
 
 `ShardedMM` owns the buffers of one problem size and offers two ways of moving the panels:
-  * "nccl": torch.distributed all_gather_into_tensor (NCCL over NVLink), written in place into the
-            full C, optionally pipelined stripe by stripe behind the compute;
   * "p2p" : the GEMM epilogue itself stores every finished tile into all ranks' C buffers over
-            NVLink (peer pointers from torch symmetric memory), followed by one barrier.
+            NVLink (peer pointers from torch symmetric memory; plain stores, no multicast), so the
+            gather overlaps the math tile by tile; one barrier afterwards makes the result visible;
+  * "nccl": torch.distributed all_gather_into_tensor (NCCL over NVLink) written in place into the
+            full C after the local panel is done -- the baseline.
+"auto" tries "p2p" and falls back to "nccl" when symmetric memory cannot be set up.
+
+The panel product itself is injectable (`mm_into`), which lets the partitioning and gathering logic
+be exercised on CPU ranks over gloo with any reference implementation of the product.
 """
+import ctypes
+
 import torch
 import torch.distributed as dist
 
-from . import ops
-from ._cabi import check, lib
+
+def _cabi_mm_into(a_rows, b, c_rows):
+    from ._cabi import check, lib
+    st = torch.cuda.current_stream(a_rows.device).cuda_stream
+    check(lib.repdl_b200_mm(a_rows.data_ptr(), b.data_ptr(), c_rows.data_ptr(), a_rows.shape[0],
+                            b.shape[1], a_rows.shape[1], 0, 0, a_rows.stride(0), b.stride(0),
+                            c_rows.stride(0), st), "mm")
 
 
 class ShardedMM:
-    def __init__(self, M, N, K, group=None, device=None, mode="nccl", stripes=1):
+    def __init__(self, M, N, K, group=None, device=None, mode="auto", mm_into=None):
         self.group = group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
         if M % self.world:
-            raise ValueError("M must be divisible by the number of ranks")
+            raise ValueError("M (%d) must be divisible by the number of ranks (%d)" % (M, self.world))
         self.M, self.N, self.K = M, N, K
         self.Mp = M // self.world
-        self.device = device or torch.device("cuda", torch.cuda.current_device())
-        self.mode = mode if self.world > 1 else "local"
-        self.stripes = stripes if (self.Mp % max(stripes, 1) == 0) else 1
-        self.C = torch.empty((M, N), dtype=torch.float32, device=self.device)
-        self.comm_stream = torch.cuda.Stream(self.device) if self.world > 1 else None
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.device = torch.device(device)
+        self.mm_into = mm_into or _cabi_mm_into
         self.kernel_launches = 0
+        self.C = None
+        self._peer_ptrs = None
+        if self.world == 1:
+            self.mode = "local"
+        elif mode in ("auto", "p2p") and self.device.type == "cuda" and mm_into is None:
+            try:
+                self._setup_p2p()
+                self.mode = "p2p"
+            except Exception as e:  # symmetric memory unavailable: use the NCCL path
+                if mode == "p2p":
+                    raise
+                self.mode, self.p2p_error = "nccl", repr(e)
+        else:
+            self.mode = "nccl"
+        if self.C is None:
+            self.C = torch.empty((M, N), dtype=torch.float32, device=self.device)
 
+    # -- layout ----------------------------------------------------------------------------------
     @property
     def row0(self):
         return self.rank * self.Mp
 
-    def _mm_into(self, a_rows, b, c_rows):
-        """c_rows[:] = a_rows @ b through the C ABI, on the current stream."""
-        st = torch.cuda.current_stream(self.device).cuda_stream
-        check(lib.repdl_b200_mm(a_rows.data_ptr(), b.data_ptr(), c_rows.data_ptr(), a_rows.shape[0],
-                                self.N, self.K, 0, 0, a_rows.stride(0), b.stride(0),
-                                c_rows.stride(0), st), "mm")
-        self.kernel_launches += 1
+    def my_rows(self):
+        return self.C[self.row0:self.row0 + self.Mp]
 
+    # -- p2p -------------------------------------------------------------------------------------
+    def _setup_p2p(self):
+        import torch.distributed._symmetric_memory as symm_mem
+        grp = self.group if self.group is not None else dist.group.WORLD
+        self.C = symm_mem.empty((self.M, self.N), dtype=torch.float32, device=self.device)
+        self._hdl = symm_mem.rendezvous(self.C, grp)
+        ptrs = [int(p) for p in self._hdl.buffer_ptrs]
+        if len(ptrs) != self.world or ptrs[self.rank] != self.C.data_ptr():
+            raise RuntimeError("unexpected symmetric-memory layout")
+        self._peer_ptrs = (ctypes.c_void_p * self.world)(*ptrs)
+        self._flag = torch.zeros(1, dtype=torch.int32, device=self.device)
+
+    def _p2p(self, a_panel, b):
+        from ._cabi import check, lib
+        st = torch.cuda.current_stream(self.device).cuda_stream
+        check(lib.repdl_b200_mm_allgather(a_panel.data_ptr(), b.data_ptr(), self._peer_ptrs,
+                                          self.world, self.row0, self.Mp, self.N, self.K, 0, 0,
+                                          a_panel.stride(0), b.stride(0), self.C.stride(0), st),
+              "mm_allgather")
+        self.kernel_launches += 1
+        # every rank's kernel (and with it its stores into this rank's C) has completed once this
+        # collective has: it is ordered after the kernel on each rank's stream
+        dist.all_reduce(self._flag, group=self.group)
+
+    # -- the product -----------------------------------------------------------------------------
     def __call__(self, a_panel, b):
         """a_panel: this rank's [M/world, K] rows of A; b: [K, N].  Returns the full [M, N] C."""
-        C, Mp = self.C, self.Mp
-        mine = C[self.row0:self.row0 + Mp]
-        if self.world == 1:
-            self._mm_into(a_panel, b, mine)
-            return C
-        if self.stripes <= 1:
-            self._mm_into(a_panel, b, mine)
-            dist.all_gather_into_tensor(C, mine, group=self.group)
-            return C
-        # stripe pipeline: stripe s is gathered on the communication stream while stripe s + 1
-        # is being computed.  Each stripe is a [world, rows, N] strided view of C, which NCCL
-        # cannot write in place, so stripes are gathered as one send/recv group per stripe.
-        cur = torch.cuda.current_stream(self.device)
-        rows = Mp // self.stripes
-        for s in range(self.stripes):
-            lo = self.row0 + s * rows
-            self._mm_into(a_panel[s * rows:(s + 1) * rows], b, C[lo:lo + rows])
-            ev = torch.cuda.Event()
-            ev.record(cur)
-            with torch.cuda.stream(self.comm_stream):
-                self.comm_stream.wait_event(ev)
-                outs = [C[r * Mp + s * rows: r * Mp + (s + 1) * rows] for r in range(self.world)]
-                dist.all_gather(outs, C[lo:lo + rows], group=self.group)
-        cur.wait_stream(self.comm_stream)
-        return C
+        if self.mode == "p2p":
+            self._p2p(a_panel, b)
+            return self.C
+        self.mm_into(a_panel, b, self.my_rows())
+        self.kernel_launches += 1
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.C, self.my_rows(), group=self.group)
+        return self.C
 
 
 def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel):
@@ -81,5 +112,5 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel):
     a_dev.copy_(a_host_panel, non_blocking=True)
     b_dev.copy_(b_host, non_blocking=True)
     C = sharded(a_dev, b_dev)
-    c_host_panel.copy_(C[sharded.row0:sharded.row0 + sharded.Mp], non_blocking=True)
+    c_host_panel.copy_(sharded.my_rows(), non_blocking=True)
     return C

@@ -1,0 +1,49 @@
+"""Worker for tests/test_gpu_multi.py: run under torchrun, one rank per GPU.  Every rank computes the
+row-sharded product in both gather modes and compares the full result, bit for bit, with the
+product it computes alone on its own GPU."""
+import json
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+sys.path.insert(0, ROOT)
+
+
+def main():
+    rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+    local = int(os.environ.get("LOCAL_RANK", rank))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    from repdl_b200 import ops
+    from repdl_b200.dist import ShardedMM
+    M, N, K = 2048, 1536, 1000
+    g = torch.Generator().manual_seed(31)
+    a = (torch.rand(M, K, generator=g) * 2 - 1).to(dev)
+    b = (torch.rand(K, N, generator=g) * 2 - 1).to(dev)
+    alone = ops.mm(a, b)
+    out = {"rank": rank}
+    for mode in ("nccl", "auto"):
+        sh = ShardedMM(M, N, K, device=dev, mode=mode)
+        for rep in range(2):
+            sh.C.zero_()
+            dist.barrier()
+            c = sh(a[sh.row0:sh.row0 + sh.Mp].contiguous(), b)
+            torch.cuda.synchronize()
+            out["%s_%d" % (mode, rep)] = bool(torch.equal(c, alone))
+        out[mode + "_mode"] = sh.mode
+        if hasattr(sh, "p2p_error"):
+            out["p2p_error"] = sh.p2p_error
+    gathered = [None] * world
+    dist.all_gather_object(gathered, out)
+    if rank == 0:
+        print("RESULT " + json.dumps(gathered), flush=True)
+    dist.barrier()
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

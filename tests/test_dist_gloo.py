@@ -1,0 +1,69 @@
+"""CPU, world_size 2 over gloo: the row-sharding and gathering logic of repdl_b200.dist.ShardedMM
+with the oracle standing in for the GPU product.  Each rank must end with the full C, bit-identical
+to the unsharded product (rows are independent chains, so sharding keeps the bits)."""
+import os
+import sys
+
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import oracle
+        from repdl_b200.dist import ShardedMM
+        g = torch.Generator().manual_seed(7)
+        M, N, K = 96, 50, 33
+        a = torch.rand(M, K, generator=g) * 2 - 1
+        b = torch.rand(K, N, generator=g) * 2 - 1
+
+        def mm_into(a_rows, bb, c_rows):
+            c_rows.copy_(oracle.mm(a_rows.contiguous(), bb))
+
+        sh = ShardedMM(M, N, K, device="cpu", mode="nccl", mm_into=mm_into)
+        assert sh.world == world and sh.Mp == M // world and sh.mode == "nccl"
+        c = sh(a[sh.row0:sh.row0 + sh.Mp], b)
+        full = oracle.mm(a, b)
+        ok = torch.equal(c.view(torch.int32), full.view(torch.int32))
+        # a rank that passes a wrong M is rejected before any communication
+        try:
+            ShardedMM(M + 1, N, K, device="cpu", mode="nccl", mm_into=mm_into)
+            ok = False
+        except ValueError:
+            pass
+        q.put((rank, ok, sh.kernel_launches))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_mm_two_ranks_gloo():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = 29500 + os.getpid() % 1000
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = sorted(q.get(timeout=120) for _ in range(world))
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert res == [(0, True, 1), (1, True, 1)]
+
+
+def test_single_process_is_local():
+    sys.path.insert(0, ROOT)
+    import oracle
+    from repdl_b200.dist import ShardedMM
+    a, b = torch.rand(8, 5), torch.rand(5, 6)
+    sh = ShardedMM(8, 6, 5, device="cpu", mm_into=lambda x, y, c: c.copy_(oracle.mm(x.contiguous(), y)))
+    assert sh.mode == "local"
+    assert torch.equal(sh(a, b), oracle.mm(a, b))
