@@ -185,48 +185,51 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
-def extras_hbm(hbm_peak, peak_kind):
-    """N = 1: the HBM-bound kernels (configs 2 and 3) with their own rooflines."""
+def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
+    """The HBM-bound kernels (configs 2 and 3) with their own rooflines, on one GPU.  At the full
+    size (2^28 elements) the outputs are also hashed and compared with the reference's hashes."""
     from repdl_b200 import ops, workloads
     out = {}
     gold_path = os.path.join(ROOT, "tests", "golden", "configs.json")
-    gold = json.load(open(gold_path)) if os.path.exists(gold_path) else None
-    n = 1 << 28
-    x = torch.cat(list(workloads.crmath_chunks(n, 1)))
-    xa = x.abs()  # on the CPU: torch's CUDA abs() would canonicalise NaN payloads
-    xd, xad = x.cuda(), xa.cuda()
-    del x, xa
-    for name, fn, key in (("div(x,10)", lambda: ops.div(xd, 10.0), "div10"),
-                          ("sqrt(|x|)", lambda: ops.sqrt(xad), "sqrt_abs"),
-                          ("exp(x)", lambda: ops.exp(xd), "exp"),
-                          ("log(|x|)", lambda: ops.log(xad), "log_abs")):
-        for _ in range(3):
+    gold = json.load(open(gold_path)) if (os.path.exists(gold_path) and n == 1 << 28) else None
+
+    def measure(fn):
+        for _ in range(warmup):
             y = fn()
         torch.cuda.synchronize()
-        ms = min(event_ms(fn) for _ in range(5))
-        rec = {"ms": ms, "GB/s": 8.0 * n / ms / 1e6, "frac_of_%s_hbm" % peak_kind: 8.0 * n / ms / 1e6 / hbm_peak,
-               "elements": n}
+        return min(event_ms(fn) for _ in range(steps)), y
+
+    if which in ("all", "crmath"):
+        x = torch.cat(list(workloads.crmath_chunks(n, 1)))
+        xa = x.abs()  # on the CPU: torch's CUDA abs() would canonicalise NaN payloads
+        xd, xad = x.cuda(), xa.cuda()
+        del x, xa
+        for name, fn, key in (("div(x,10)", lambda: ops.div(xd, 10.0), "div10"),
+                              ("sqrt(|x|)", lambda: ops.sqrt(xad), "sqrt_abs"),
+                              ("exp(x)", lambda: ops.exp(xd), "exp"),
+                              ("log(|x|)", lambda: ops.log(xad), "log_abs")):
+            ms, y = measure(fn)
+            rec = {"ms": ms, "GB/s": 8.0 * n / ms / 1e6,
+                   "frac_of_%s_hbm" % peak_kind: 8.0 * n / ms / 1e6 / hbm_peak, "elements": n}
+            if gold:
+                rec["sha256_equal_reference_cpu"] = (
+                    hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
+                    == gold["c2_crmath_2p28"]["whole"][key])
+            out[name] = rec
+            del y
+        del xd, xad
+        torch.cuda.empty_cache()
+    if which in ("all", "sums"):
+        # rows x 4096 matrix from the first n elements of the config-3 stream
+        rows = n // 4096
+        r = torch.cat(list(workloads.sum_chunks(rows * 4096, 2))).view(rows, 4096).cuda()
+        ms, y = measure(lambda: ops.sum2d_dim1(r))
+        rec = {"ms": ms, "GB/s": 4.0 * r.numel() / ms / 1e6,
+               "frac_of_%s_hbm" % peak_kind: 4.0 * r.numel() / ms / 1e6 / hbm_peak}
         if gold:
-            rec["sha256_equal_reference_cpu"] = (
-                hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
-                == gold["c2_crmath_2p28"]["whole"][key])
-        out[name] = rec
-        del y
-    del xd, xad
-    torch.cuda.empty_cache()
-    # sums: rows 65536 x 4096 (the first 2^28 elements of the config-3 stream)
-    r = torch.cat(list(workloads.sum_chunks(1 << 28, 2))).view(65536, 4096).cuda()
-    fn = lambda: ops.sum2d_dim1(r)  # noqa: E731
-    for _ in range(3):
-        y = fn()
-    torch.cuda.synchronize()
-    ms = min(event_ms(fn) for _ in range(5))
-    rec = {"ms": ms, "GB/s": 4.0 * r.numel() / ms / 1e6,
-           "frac_of_%s_hbm" % peak_kind: 4.0 * r.numel() / ms / 1e6 / hbm_peak}
-    if gold:
-        rec["sha256_equal_reference_cpu"] = (hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
-                                             == gold["c3_sum_rows_65536x4096"]["sha256"])
-    out["sum rows [65536,4096]"] = rec
+            rec["sha256_equal_reference_cpu"] = (hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
+                                                 == gold["c3_sum_rows_65536x4096"]["sha256"])
+        out["sum rows [%d,4096]" % rows] = rec
     return out
 
 
@@ -240,6 +243,10 @@ def main():
     ap.add_argument("--mode", default="auto", choices=["auto", "nccl", "p2p"])
     ap.add_argument("--ref-rows", type=int, default=16)
     ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--workload", default="mm", choices=["mm", "crmath", "sums"],
+                    help="mm: the headline product; crmath / sums: only the HBM-bound kernels of "
+                         "configs 2 / 3 at --elements (used for profiling captures)")
+    ap.add_argument("--elements", type=int, default=1 << 28)
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
     args = ap.parse_args()
@@ -255,6 +262,15 @@ def main():
     import torch.distributed as dist
     from repdl_b200 import workloads
     from repdl_b200.dist import ShardedMM, mm_from_host
+
+    if args.workload != "mm":
+        if rank == 0:
+            torch.cuda.set_device(local_rank)
+            hbm_peak, peak_kind = measured_peaks()
+            print(json.dumps({"workload": args.workload, "elements": args.elements,
+                              "results": extras_hbm(hbm_peak, peak_kind, args.elements, args.workload,
+                                                    args.steps, args.warmup)}), flush=True)
+        return
 
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)

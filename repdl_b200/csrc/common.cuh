@@ -29,6 +29,9 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 // Number of SMs of the current device (cached per thread; 148 on B200).
 int sm_count();
 
+// The plain single-thread chain walk of sum1d.cu for short chains (no scratch): out[0] = factor * chain.
+int sum1d_plain(const float *x, float *out, int64_t n, float factor, cudaStream_t st);
+
 __device__ __forceinline__ float4 ldg_f4(const float *p)
 {
     return __ldg(reinterpret_cast<const float4 *>(p));

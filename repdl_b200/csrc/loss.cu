@@ -97,5 +97,5 @@ extern "C" int repdl_b200_cross_entropy(const float *x, const int64_t *target, f
     // mean over rows: the same single chain as sum1d with factor float(1.0 / M)
     // (backend/cpu/summation.cpp:15)
     const float factor = (float)(1.0 / (double)M);
-    return repdl_b200_sum1d(row_scratch, loss, M, factor, nullptr, 0, stream);
+    return sum1d_plain(row_scratch, loss, M, factor, (cudaStream_t)stream);
 }

@@ -33,6 +33,14 @@ namespace {
 #ifndef REPDL_MM_MINB_BIG
 #define REPDL_MM_MINB_BIG 1
 #endif
+#ifndef REPDL_MM_KUNROLL
+#define REPDL_MM_KUNROLL REPDL_MM_BK  // k-steps of a slab unrolled back to back
+#endif
+#ifndef REPDL_MM_GROUP
+#define REPDL_MM_GROUP 8
+#endif
+#define REPDL_PRAGMA(x) _Pragma(#x)
+#define REPDL_UNROLL(n) REPDL_PRAGMA(unroll n)
 constexpr int BK = REPDL_MM_BK;
 
 // Cooperative loader for one operand slab of BX (rows or columns of C) x BK (k).
@@ -122,7 +130,7 @@ struct SlabLoader {
 // tiles are visited in groups of GROUP tile-rows, column by column inside a group.
 __device__ __forceinline__ void tile_of_cta(int pid, int tilesM, int tilesN, int &tm, int &tn)
 {
-    constexpr int GROUP = 8;
+    constexpr int GROUP = REPDL_MM_GROUP;
     int per_group = GROUP * tilesN;
     int g = pid / per_group;
     int first = g * GROUP;
@@ -202,7 +210,7 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
             la.load(A, lda, m0, (kt + 1) * BK, M, K, -0.0f, t);
             lb.load(B, ldb, n0, (kt + 1) * BK, N, K, 0.0f, t);
         }
-#pragma unroll
+        REPDL_UNROLL(REPDL_MM_KUNROLL)
         for (int k = 0; k < BK; k++) {
             if constexpr (kF2) {
                 unsigned long long a[TM], b[TN / 2];  // a[i] = (a_i, a_i); b[p] = (b_2p, b_2p+1)

@@ -157,7 +157,7 @@ sum_cols_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t M,
 }
 
 // ------------------------------------------------------------------------------------------------
-// One long chain per CTA (sum1d: a single CTA; sum4d_dim023: one CTA per channel).  The chain is
+// One long chain per CTA (sum4d_dim023: one CTA per channel; sum1d lives in sum1d.cu).  The chain is
 // the concatenation of `nseg` contiguous segments of `seglen` floats, segment s starting at
 // base + s * segstride.  All threads stage the next TILE chain elements into shared memory while
 // thread 0 walks the current tile with LDS.128 + four dependent adds; the walk (4 cycles per
@@ -220,24 +220,6 @@ chain_sum_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t n
 }  // namespace repdl_b200
 
 using namespace repdl_b200;
-
-extern "C" size_t repdl_b200_sum1d_scratch_bytes(int64_t n)
-{
-    (void)n;
-    return 256;
-}
-
-extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float factor, void *scratch,
-                                size_t scratch_bytes, void *stream)
-{
-    clear_stale_error();
-    if (n < 0) return REPDL_E_SHAPE;
-    if (!out || (n > 0 && !x)) return REPDL_E_NULL;
-    (void)scratch;
-    (void)scratch_bytes;
-    chain_sum_kernel<<<1, CHAIN_THREADS, 0, (cudaStream_t)stream>>>(x, out, 1, n, 0, 0, factor);
-    return launch_status();
-}
 
 extern "C" int repdl_b200_sum2d_dim0(const float *x, float *out, int64_t M, int64_t N, float factor,
                                      void *stream)

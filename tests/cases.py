@@ -115,6 +115,51 @@ def build_cases():
         x[0] = 1048576.0
         return (x, False)
     cases.append(("sum1d_hover", "sum1d", mk_hover))
+
+    # long chains (the summarised path): the same stress patterns at sizes above one node
+    def mk_long(seed, n, scale, first=None, dist="normal"):
+        def mk():
+            g = _g(seed)
+            if dist == "normal":
+                x = torch.randn(n, generator=g) * scale
+            elif dist == "lognormal":
+                x = torch.empty(n).log_normal_(0, 2, generator=g) * (torch.randint(0, 2, (n,), generator=g).float() * 2 - 1)
+            elif dist == "halves":      # every add is an exact tie once |s| is in [2^23, 2^24)
+                x = (torch.randint(-8, 8, (n,), generator=g).float() + 0.5)
+            elif dist == "wide":        # magnitudes spread over 60 binades
+                x = torch.randn(n, generator=g) * torch.exp2(torch.randint(-30, 30, (n,), generator=g).float())
+            elif dist == "tiny":        # mostly absorbed
+                x = torch.randn(n, generator=g) * 1e-3
+            if first is not None:
+                x[0] = first
+            return (x, False)
+        return mk
+    cases.append(("sum1d_long_normal", "sum1d", mk_long(730, 300001, 100.0)))
+    cases.append(("sum1d_long_lognormal", "sum1d", mk_long(731, 1 << 20, 1.0, dist="lognormal")))
+    cases.append(("sum1d_long_hover_up", "sum1d", mk_long(732, 500000, 3.0, first=1048576.0)))
+    cases.append(("sum1d_long_hover_neg", "sum1d", mk_long(733, 500000, 3.0, first=-2097152.0)))
+    cases.append(("sum1d_long_ties", "sum1d", mk_long(734, 400000, 1.0, first=12000000.0, dist="halves")))
+    cases.append(("sum1d_long_ties_neg", "sum1d", mk_long(735, 400000, 1.0, first=-9000000.0, dist="halves")))
+    cases.append(("sum1d_long_wide", "sum1d", mk_long(736, 400000, 1.0, dist="wide")))
+    cases.append(("sum1d_long_absorbed", "sum1d", mk_long(737, 700000, 1.0, first=4.0e6, dist="tiny")))
+    cases.append(("sum1d_long_signflips", "sum1d", mk_long(738, 300000, 1.0e-3)))
+
+    def mk_long_cancel():
+        x = _randn(739, 400000, scale=1e6)
+        x[::2] = -x[1::2] * (1 + 2 ** -20)
+        return (x, True)
+    cases.append(("sum1d_long_cancel_mean", "sum1d", mk_long_cancel))
+
+    def mk_long_inf():
+        x = _randn(740, 200000, scale=10.0)
+        x[150000] = float("inf")
+        return (x, False)
+    cases.append(("sum1d_long_inf", "sum1d", mk_long_inf))
+
+    def mk_long_subnormal():
+        x = _randn(741, 200000, scale=1e-41)   # subnormal inputs: the state stays below 2^-104
+        return (x, False)
+    cases.append(("sum1d_long_subnormal", "sum1d", mk_long_subnormal))
     for (M, N) in [(1, 1), (37, 53), (256, 10), (256, 128), (130, 4096), (5, 4100), (1, 7), (9, 1)]:
         for kd in (False, True):
             for avg in (False, True):

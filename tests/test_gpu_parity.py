@@ -132,3 +132,25 @@ def test_mm_linearity_in_rows(ops):
     full = ops.mm(a, b)
     for lo, hi in [(0, 256), (256, 1024), (1024, 1029), (1029, 2048)]:
         assert torch.equal(full[lo:hi], ops.mm(a[lo:hi], b))
+
+
+def test_config3_full_chain_and_rows(ops):
+    """Config 3 at full size: the 2^30-element chain (checked against the reference's running
+    state after every quarter and at the end) and the [65536, 4096] row sums."""
+    path = os.path.join(GOLDEN, "configs.json")
+    if not os.path.exists(path):
+        pytest.skip("configs.json not generated")
+    from repdl_b200 import workloads
+    gold = golden("configs.json")
+    states = gold["c3_sum1d_2p30"]["state_after_chunk_hex"]
+    x = torch.empty(1 << 30, dtype=torch.float32, device="cuda")
+    for ci, chunk in enumerate(workloads.sum_chunks(1 << 30, 2)):
+        x[ci << 24:(ci + 1) << 24] = chunk.cuda()
+
+    def hexof(t):
+        return "%08x" % (t.cpu().view(torch.int32).item() & 0xFFFFFFFF)
+    for nchunks in (1, 16, 32, 48, 64):
+        assert hexof(ops.sum1d(x[:nchunks << 24])) == states[nchunks - 1], nchunks
+    assert hexof(ops.sum1d(x)) == gold["c3_sum1d_2p30"]["result_hex"] == "c975c2b7"
+    rows = ops.sum2d_dim1(x[:1 << 28].view(65536, 4096))
+    assert sha(rows) == gold["c3_sum_rows_65536x4096"]["sha256"]
