@@ -230,6 +230,17 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
             rec["sha256_equal_reference_cpu"] = (hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
                                                  == gold["c3_sum_rows_65536x4096"]["sha256"])
         out["sum rows [%d,4096]" % rows] = rec
+        # the same elements as ONE chain (config 3's 1-D case is this stream continued to 2^30)
+        flat = r.view(-1)
+        ms, y = measure(lambda: ops.sum1d(flat))
+        rec = {"ms": ms, "GB/s": 4.0 * flat.numel() / ms / 1e6,
+               "frac_of_%s_hbm" % peak_kind: 4.0 * flat.numel() / ms / 1e6 / hbm_peak,
+               "elements": flat.numel()}
+        if gold and flat.numel() % (1 << 24) == 0:
+            want = gold["c3_sum1d_2p30"]["state_after_chunk_hex"][flat.numel() // (1 << 24) - 1]
+            rec["bits_equal_reference_cpu"] = (
+                "%08x" % (y.cpu().view(torch.int32).item() & 0xFFFFFFFF)) == want
+        out["sum1d chain [%d]" % flat.numel()] = rec
     return out
 
 

@@ -7,8 +7,9 @@
 // x = q*u gives exactly m' = m + rint(q), rint = round-half-even; on an exact tie (q = n + 1/2) the
 // result is whichever of m+n, m+n+1 is even, i.e. it depends on the parity of m.  So, for a fixed
 // binade hypothesis E, a run of elements acts on m as  m -> m + D[parity of m]  -- two integers --
-// and the run is VALID for a given incoming m iff every intermediate state stays strictly inside
-// (2^23, 2^24): m + lo > 2^23 and m + hi < 2^24 with lo/hi the extreme prefix increments.  Such
+// and the run is VALID for a given incoming m iff no step's exact value falls below 2^23 (there the
+// grid is finer) and no state reaches 2^24: m + lo >= 2^23 and m + hi < 2^24, with lo the minimum
+// over the steps of (increment so far + floor(q)) and hi the maximum prefix increment.  Such
 // summaries (D0, D1, lo, hi) compose associatively, so they can be built by a tree in parallel.
 // (For s < 0 the same summary applies to |m| with all four numbers negated and lo/hi swapped.)
 //
@@ -93,14 +94,17 @@ __device__ __forceinline__ Summ leaf_summary(const float (&v)[LEAF], int E)
     const float MAGIC = 12582912.0f;                       // 1.5 * 2^23: q + MAGIC rounds q to an integer
     int d0 = 0, delta = 0;                                 // d1 = d0 + delta, |delta| <= 1
     int lo = BIGI, hi = -BIGI;
-    bool bad = false;
+    bool bad = false, tie_seen = false;
 #pragma unroll
     for (int i = 0; i < LEAF; i++) {
         const float q = __fmul_rn(v[i], scale);            // exact (power of two) unless it overflows
         bad |= !(fabsf(q) < 4194304.0f);                   // |q| >= 2^22, inf or NaN: not summarised
         const float t = __fadd_rn(q, MAGIC);
         int R = __float_as_int(t) - 0x4B400000;            // rint(q), ties to even
-        const float d = __fsub_rn(q, __fsub_rn(t, MAGIC)); // q - rint(q), exact
+        const float d = __fsub_rn(q, __fsub_rn(t, MAGIC)); // q - rint(q), exact, in [-0.5, 0.5]
+        // The step is modelled correctly iff its exact value m + q is not below 2^23, i.e. iff
+        // m + D_before + floor(q) >= 2^23 (m and D are integers); floor(q) = R - (d < 0).
+        lo = min(lo, d0 + R + (__float_as_int(d) >> 31));
         if (fabsf(d) == 0.5f && !bad) {
             // exact tie: the result is the even one of m+n, m+n+1 with n = floor(q)
             const int n = d > 0.0f ? R : R - 1;
@@ -108,13 +112,15 @@ __device__ __forceinline__ Summ leaf_summary(const float (&v)[LEAF], int E)
             const int inc1 = n + ((1 + d0 + delta + n) & 1);
             delta += inc1 - inc0;
             R = inc0;
+            tie_seen = true;
         }
         d0 += R;
-        lo = min(lo, d0);
         hi = max(hi, d0);
     }
     if (bad) return summ_invalid();
-    return {d0, d0 + delta, lo - 1, hi + 1};  // +-1: covers the odd-parity track (|delta| <= 1)
+    // after a tie the odd-parity track may run one off the even one: widen by 1 to cover both
+    const int margin = tie_seen ? 1 : 0;
+    return {d0, d0 + delta, lo - margin, hi + margin};
 }
 
 __device__ __forceinline__ int exp_field(float s) { return (__float_as_int(s) >> 23) & 0xFF; }
@@ -133,7 +139,7 @@ __device__ __forceinline__ float apply_inc(float s, int inc)
 //   open(j, s)       -> the exact state after child j entered with state s (uniform call).
 // Returns the exact state after all children.
 template <class Get, class Open>
-__device__ __forceinline__ float walk_level(float s, int count, Get get, Open open)
+__device__ __forceinline__ float walk_level(float s, int count, Get get, Open open, int &opens)
 {
     const int lane = threadIdx.x & 31;
     int pos = 0;
@@ -159,7 +165,7 @@ __device__ __forceinline__ float walk_level(float s, int count, Get get, Open op
                 ok = false;
             } else {
                 const int m_in = m + (par ? excl.d1 : excl.d0);
-                ok = (m_in + mine.lo > M_LO) && (m_in + mine.hi < M_HI);
+                ok = (m_in + mine.lo >= M_LO) && (m_in + mine.hi < M_HI);
             }
         }
         const unsigned badmask = __ballot_sync(0xffffffffu, !ok);
@@ -171,6 +177,7 @@ __device__ __forceinline__ float walk_level(float s, int count, Get get, Open op
         const Summ before = shfl_summ(excl, j);  // valid: every lane in [pos, j) checked ok
         if (j > pos) s = apply_inc(s, par ? before.d1 : before.d0);
         s = open(j, s);
+        opens++;
         pos = j + 1;
     }
     return s;
@@ -339,10 +346,11 @@ __global__ void __launch_bounds__(32)
 walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__restrict__ hyp,
             const int4 *__restrict__ tileA, const int4 *__restrict__ tileB,
             const int4 *__restrict__ nodeA, const int4 *__restrict__ nodeB, float factor,
-            float *__restrict__ out, int vec)
+            float *__restrict__ out, int vec, int *__restrict__ stats)
 {
     const int lane = threadIdx.x;
     float s = 0.0f;
+    int node_opens = 0, tile_opens = 0, leaf_opens = 0;
     for (int g0 = 0; g0 < nnodes; g0 += 32) {
         const int count = min(32, nnodes - g0);
         const int node = g0 + lane;
@@ -380,11 +388,18 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
                                     for (int i = 0; i < LEAF; i++) r = __fadd_rn(r, v[i]);
                                 }
                                 return __shfl_sync(0xffffffffu, r, jl);
-                            });
-                    });
-            });
+                            },
+                            leaf_opens);
+                    },
+                    tile_opens);
+            },
+            node_opens);
     }
-    if (lane == 0) out[0] = __fmul_rn(factor, s);
+    if (lane == 0) {
+        out[0] = __fmul_rn(factor, s);
+        // how many nodes / tiles / leaves had to be opened (diagnostics, first 16 bytes of scratch)
+        stats[0] = node_opens, stats[1] = tile_opens, stats[2] = leaf_opens, stats[3] = nnodes;
+    }
 }
 
 // Short chains: one thread walks shared-memory tiles that the rest of the CTA stages.
@@ -428,7 +443,7 @@ constexpr int64_t kShortChain = 1 << 16;  // below this the plain walk is faster
 
 struct Layout {
     int64_t nnodes;
-    size_t off_sum, off_hyp, off_nodeA, off_nodeB, off_tileA, off_tileB, total;
+    size_t off_stats, off_sum, off_hyp, off_nodeA, off_nodeB, off_tileA, off_tileB, total;
 };
 
 Layout layout_for(int64_t n)
@@ -437,6 +452,7 @@ Layout layout_for(int64_t n)
     L.nnodes = (n + NODE - 1) / NODE;
     auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
     size_t o = 0;
+    L.off_stats = o; o = up(o + 4 * sizeof(int));
     L.off_sum = o;   o = up(o + (size_t)L.nnodes * sizeof(double));
     L.off_hyp = o;   o = up(o + (size_t)L.nnodes * sizeof(int2));
     L.off_nodeA = o; o = up(o + (size_t)L.nnodes * sizeof(int4));
@@ -493,6 +509,7 @@ extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float fac
     if ((e = launch_status())) return e;
     summarise_kernel<<<nn, 256, 0, st>>>(x, n, hyp, tileA, tileB, nodeA, nodeB, vec);
     if ((e = launch_status())) return e;
-    walk_kernel<<<1, 32, 0, st>>>(x, n, (int)nn, hyp, tileA, tileB, nodeA, nodeB, factor, out, vec);
+    walk_kernel<<<1, 32, 0, st>>>(x, n, (int)nn, hyp, tileA, tileB, nodeA, nodeB, factor, out, vec,
+                                  reinterpret_cast<int *>(base + L.off_stats));
     return launch_status();
 }
