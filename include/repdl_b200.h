@@ -88,7 +88,7 @@ int repdl_b200_conv2d_grad_kernel(const float *grad_output, const float *input,
  *
  * sum1d reproduces one chain of n elements without walking it element by element (per-binade
  * integer summaries, see csrc/sum1d.cu).  It needs scratch: pass a buffer of at least
- * repdl_b200_sum1d_scratch_bytes(n) bytes (0 for short chains; about n/32 bytes otherwise),
+ * repdl_b200_sum1d_scratch_bytes(n) bytes (0 for short chains; about n/600 bytes otherwise),
  * 256-byte aligned; its contents on entry do not matter and it may be reused by the next call
  * on the same stream (calls that overlap on the GPU must not share it). */
 size_t repdl_b200_sum1d_scratch_bytes(int64_t n);

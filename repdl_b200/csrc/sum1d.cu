@@ -8,8 +8,8 @@
 // result is whichever of m+n, m+n+1 is even, i.e. it depends on the parity of m.  So, for a fixed
 // binade hypothesis E, a run of elements acts on m as  m -> m + D[parity of m]  -- two integers --
 // and the run is VALID for a given incoming m iff no step's exact value falls below 2^23 (there the
-// grid is finer) and no state reaches 2^24: m + lo >= 2^23 and m + hi < 2^24, with lo the minimum
-// over the steps of (increment so far + floor(q)) and hi the maximum prefix increment.  Such
+// grid is finer) and no state reaches 2^24: m + lo >= 2^23 and m + hi < 2^24, with lo / hi the
+// minimum / maximum over the steps of (increment so far + floor(q) / ceil(q)).  Such
 // summaries (D0, D1, lo, hi) compose associatively, so they can be built by a tree in parallel.
 // (For s < 0 the same summary applies to |m| with all four numbers negated and lo/hi swapped.)
 //
@@ -19,14 +19,18 @@
 //                           start, and from it two binade hypotheses per node: the predicted
 //                           binade and its nearer neighbour
 //   3. summarise_kernel     per node: leaf summaries (32 elements per lane) under both hypotheses,
-//                           composed to one summary per tile of 1024 elements and per node
-//   4. walk_kernel          ONE warp carries the exact fp32 state through the nodes: 32 node
+//                           composed (in order) to one summary per node
+//   4. walk_kernel          one CTA; warp 0 carries the exact fp32 state through the nodes: 32 node
 //                           summaries are composed by a warp scan and applied in one step when
 //                           they are valid for the exact state; the first node that is not valid
 //                           (a real binade change, a wrong prediction, a huge element, inf/NaN) is
-//                           opened: its 32 tiles are handled the same way, an invalid tile is
-//                           loaded and its 32 leaves are summarised on the fly under the exact
-//                           binade, and an invalid leaf is finally walked with 32 real fp32 adds.
+//                           opened: all 32 warps stage its 32 tiles in shared memory and summarise
+//                           them under the exact binade and its nearer neighbour, warp 0 walks the
+//                           tiles the same way, an invalid tile has its 32 leaves summarised on the
+//                           fly, and an invalid leaf is finally walked with 32 real fp32 adds.
+//                           After an opened child the scan is not redone: its prefix increments are
+//                           re-anchored on the new exact state (valid while binade, sign and --
+//                           where ties follow -- parity are unchanged).
 // A wrong prediction therefore costs time, never bits: every summary is applied only after its
 // validity has been checked against the exact state, and everything else is real fp32 addition.
 // Elements past n are treated as +0.0f, which never changes a chain that started at +0 (such a
@@ -102,9 +106,14 @@ __device__ __forceinline__ Summ leaf_summary(const float (&v)[LEAF], int E)
         const float t = __fadd_rn(q, MAGIC);
         int R = __float_as_int(t) - 0x4B400000;            // rint(q), ties to even
         const float d = __fsub_rn(q, __fsub_rn(t, MAGIC)); // q - rint(q), exact, in [-0.5, 0.5]
-        // The step is modelled correctly iff its exact value m + q is not below 2^23, i.e. iff
-        // m + D_before + floor(q) >= 2^23 (m and D are integers); floor(q) = R - (d < 0).
-        lo = min(lo, d0 + R + (__float_as_int(d) >> 31));
+        // The step is modelled correctly iff its exact value m + q is not below 2^23 (there the
+        // grid is finer), i.e. iff m + D_before + floor(q) >= 2^23 (m and D are integers).  For a
+        // negative state the same condition reads |m| - (D_before + ceil(q)) >= 2^23, so `hi`
+        // tracks D_before + ceil(q): it bounds the reachable states from above (within one unit)
+        // and becomes the exact lower bound when the summary is negated.
+        const int fl = d0 + R + (__float_as_int(d) >> 31);  // D_before + floor(q) (an element of -0.0f gives d = -0 and a bound one unit too careful)
+        lo = min(lo, fl);
+        hi = max(hi, fl + (d != 0.0f ? 1 : 0));             // D_before + ceil(q)
         if (fabsf(d) == 0.5f && !bad) {
             // exact tie: the result is the even one of m+n, m+n+1 with n = floor(q)
             const int n = d > 0.0f ? R : R - 1;
@@ -115,7 +124,6 @@ __device__ __forceinline__ Summ leaf_summary(const float (&v)[LEAF], int E)
             tie_seen = true;
         }
         d0 += R;
-        hi = max(hi, d0);
     }
     if (bad) return summ_invalid();
     // after a tie the odd-parity track may run one off the even one: widen by 1 to cover both
@@ -133,49 +141,69 @@ __device__ __forceinline__ float apply_inc(float s, int inc)
     return __int_as_float((int)((b & 0xFF800000u) | ((unsigned)m & 0x7FFFFFu)));
 }
 
-// One level of the walk.  `count` children (<= 32), child c owned by lane c.
+// One level of the walk, run by one full warp.  `count` children (<= 32), child c owned by lane c.
 //   get(E, negative) -> this lane's summary for a state in binade E (already negated for s < 0),
 //                       or an invalid summary;
-//   open(j, s)       -> the exact state after child j entered with state s (uniform call).
+//   open(j, s)       -> the exact state after child j entered with state s (warp-uniform call).
 // Returns the exact state after all children.
 template <class Get, class Open>
 __device__ __forceinline__ float walk_level(float s, int count, Get get, Open open, int &opens)
 {
     const int lane = threadIdx.x & 31;
     int pos = 0;
+    // context of the last scan: summaries, assumed cumulative increment c (from pos0 to this lane's
+    // start, for start parity par0), start state m0
+    Summ mine = summ_identity(), incl = summ_identity();
+    int c = 0, m0 = 0, pos0 = 0, scanE = -1;
+    bool scanNeg = false, have = false;
+    unsigned tiemask = 0, invmask = 0;
     while (pos < count) {
         const int E = exp_field(s);
         const bool neg = __float_as_int(s) < 0;
-        Summ mine = (lane >= pos && lane < count) ? get(E, neg) : summ_identity();
-        if (E < 24 || E > 253) mine = (lane >= pos && lane < count) ? summ_invalid() : summ_identity();
-        // inclusive scan of composition over the lanes
-        Summ incl = mine;
-#pragma unroll
-        for (int dlt = 1; dlt < 32; dlt <<= 1) {
-            Summ up = shfl_up_summ(incl, dlt);
-            if (lane >= dlt) incl = summ_compose(up, incl);
-        }
-        Summ excl = shfl_up_summ(incl, 1);
-        if (lane == 0) excl = summ_identity();
         const int m = (int)(((unsigned)__float_as_int(s) & 0x7FFFFFu) | 0x800000u);
-        const int par = m & 1;
+        const unsigned from_pos = 0xFFFFFFFFu << pos;
+        bool reuse = have && E == scanE && neg == scanNeg &&
+                     (invmask & (0xFFFFFFFFu << pos0) & ~from_pos) == 0u;
+        int delta = 0;
+        if (reuse) {
+            const int a_pos = m0 + __shfl_sync(0xffffffffu, c, pos);
+            // a different parity changes the outcome of later ties
+            if (((m ^ a_pos) & 1) && (tiemask & from_pos)) reuse = false;
+            delta = m - a_pos;
+        }
+        if (!reuse) {
+            const bool active = lane >= pos && lane < count;
+            mine = active ? ((E < 24 || E > 253) ? summ_invalid() : get(E, neg)) : summ_identity();
+            incl = mine;
+#pragma unroll
+            for (int dlt = 1; dlt < 32; dlt <<= 1) {
+                Summ up = shfl_up_summ(incl, dlt);
+                if (lane >= dlt) incl = summ_compose(up, incl);
+            }
+            const int par0 = m & 1;
+            const int incd = par0 ? incl.d1 : incl.d0;
+            c = __shfl_up_sync(0xffffffffu, incd, 1);
+            if (lane <= pos) c = 0;
+            m0 = m, pos0 = pos, scanE = E, scanNeg = neg, have = true, delta = 0;
+            tiemask = __ballot_sync(0xffffffffu, active && mine.d0 != mine.d1);
+            invmask = __ballot_sync(0xffffffffu, active && summ_is_invalid(mine));
+        }
+        // lanes after an invalid lane carry a meaningless c; they are never reached before a rescan
+        const int m_in = m0 + c + delta;
         bool ok = true;
         if (lane >= pos && lane < count) {
-            if (summ_is_invalid(excl) || summ_is_invalid(mine)) {
-                ok = false;
-            } else {
-                const int m_in = m + (par ? excl.d1 : excl.d0);
-                ok = (m_in + mine.lo >= M_LO) && (m_in + mine.hi < M_HI);
-            }
+            ok = !summ_is_invalid(mine) && ((invmask & (0xFFFFFFFFu << pos0) & ~(0xFFFFFFFFu << lane)) == 0u) &&
+                 (m_in + mine.lo >= M_LO) && (m_in + mine.hi < M_HI);
         }
         const unsigned badmask = __ballot_sync(0xffffffffu, !ok);
         if (badmask == 0u) {
-            const Summ tot = shfl_summ(incl, 31);
-            return apply_inc(s, par ? tot.d1 : tot.d0);
+            // all remaining children valid: total increment = prefix through the last lane
+            const int par0 = m0 & 1;
+            const int tot = __shfl_sync(0xffffffffu, par0 ? incl.d1 : incl.d0, 31);
+            return apply_inc(s, (m0 + tot + delta) - m);
         }
         const int j = __ffs((int)badmask) - 1;
-        const Summ before = shfl_summ(excl, j);  // valid: every lane in [pos, j) checked ok
-        if (j > pos) s = apply_inc(s, par ? before.d1 : before.d0);
+        if (j > pos) s = apply_inc(s, __shfl_sync(0xffffffffu, m_in, j) - m);
         s = open(j, s);
         opens++;
         pos = j + 1;
@@ -280,7 +308,7 @@ node_scan_kernel(const double *__restrict__ node_sum, int nnodes, int2 *__restri
 }
 
 // ---------------------------------------------------------------------------------------------
-// 3. summaries of tiles and nodes under both hypotheses
+// 3. node summaries under both hypotheses
 // ---------------------------------------------------------------------------------------------
 __device__ __forceinline__ Summ warp_reduce_summ(Summ s)
 {
@@ -297,8 +325,7 @@ __device__ __forceinline__ Summ warp_reduce_summ(Summ s)
 
 __global__ void __launch_bounds__(256)
 summarise_kernel(const float *__restrict__ x, int64_t n, const int2 *__restrict__ hyp,
-                 int4 *__restrict__ tileA, int4 *__restrict__ tileB, int4 *__restrict__ nodeA,
-                 int4 *__restrict__ nodeB, int vec)
+                 int4 *__restrict__ nodeA, int4 *__restrict__ nodeB, int vec)
 {
     __shared__ Summ sA[32], sB[32];
     const int node = blockIdx.x;
@@ -312,8 +339,6 @@ summarise_kernel(const float *__restrict__ x, int64_t n, const int2 *__restrict_
         if (lane == 0) {
             sA[tl] = a;
             sB[tl] = b;
-            tileA[(int64_t)node * 32 + tl] = make_int4(a.d0, a.d1, a.lo, a.hi);
-            tileB[(int64_t)node * 32 + tl] = make_int4(b.d0, b.d1, b.lo, b.hi);
         }
     }
     __syncthreads();
@@ -328,52 +353,117 @@ summarise_kernel(const float *__restrict__ x, int64_t n, const int2 *__restrict_
 }
 
 // ---------------------------------------------------------------------------------------------
-// 4. the walk (one warp)
+// 4. the walk: one CTA; warp 0 walks, all warps prepare an opened node
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ Summ pick(int E, bool neg, int2 h, int4 a, int4 b)
+__device__ __forceinline__ Summ pick(int E, bool neg, int e0, int e1, const Summ &a, const Summ &b)
 {
     Summ s;
-    if (E == h.x)
-        s = {a.x, a.y, a.z, a.w};
-    else if (E == h.y)
-        s = {b.x, b.y, b.z, b.w};
+    if (E == e0)
+        s = a;
+    else if (E == e1)
+        s = b;
     else
         return summ_invalid();
     return neg ? summ_negate(s) : s;
 }
 
-__global__ void __launch_bounds__(32)
+constexpr int WALK_THREADS = 512;   // 16 warps: each prepares two tiles of an opened node
+constexpr int RUN_PITCH = 36;  // floats per lane-run in shared memory: LDS.128 without bank conflicts
+struct WalkShared {
+    float raw[32][32 * RUN_PITCH];  // the 32 tiles of the opened node
+    Summ tile[2][32];               // tile summaries under the two binades of `e`
+    int e[2];
+    int cmd;                        // node to open, or -1: finished
+};
+constexpr int WALK_SMEM_BYTES = (int)sizeof(WalkShared);
+
+__device__ __forceinline__ void cta_bar(int id)
+{
+    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(WALK_THREADS) : "memory");
+}
+
+// All warps: stage the 32 tiles of node nd in shared memory and summarise them under sh.e[0..1].
+__device__ __forceinline__ void prepare_node(WalkShared &sh, const float *__restrict__ x, int64_t n,
+                                             int nd, bool vec)
+{
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    for (int tl = warp; tl < 32; tl += WALK_THREADS / 32) {
+        float v[LEAF];
+        load_leaf(x, n, (int64_t)nd * NODE + (int64_t)tl * TILE, vec, v);
+        float4 *dst = reinterpret_cast<float4 *>(&sh.raw[tl][lane * RUN_PITCH]);
+#pragma unroll
+        for (int i = 0; i < LEAF / 4; i++)
+            dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+        Summ a = warp_reduce_summ(leaf_summary(v, sh.e[0]));
+        Summ b = warp_reduce_summ(leaf_summary(v, sh.e[1]));
+        if (lane == 0) {
+            sh.tile[0][tl] = a;
+            sh.tile[1][tl] = b;
+        }
+    }
+}
+
+__global__ void __launch_bounds__(WALK_THREADS, 1)
 walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__restrict__ hyp,
-            const int4 *__restrict__ tileA, const int4 *__restrict__ tileB,
             const int4 *__restrict__ nodeA, const int4 *__restrict__ nodeB, float factor,
             float *__restrict__ out, int vec, int *__restrict__ stats)
 {
-    const int lane = threadIdx.x;
+    extern __shared__ __align__(16) unsigned char walk_smem[];
+    WalkShared &sh = *reinterpret_cast<WalkShared *>(walk_smem);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+    if (warp != 0) {
+        // helpers: wait for a node to prepare until the walker says it is done
+        while (true) {
+            cta_bar(1);
+            const int nd = sh.cmd;
+            if (nd < 0) break;
+            prepare_node(sh, x, n, nd, vec != 0);
+            cta_bar(2);
+        }
+        return;
+    }
+
     float s = 0.0f;
     int node_opens = 0, tile_opens = 0, leaf_opens = 0;
     for (int g0 = 0; g0 < nnodes; g0 += 32) {
         const int count = min(32, nnodes - g0);
         const int node = g0 + lane;
         int2 h = make_int2(0, 0);
-        int4 na = make_int4(0, 0, 0, 0), nb = na;
+        Summ na = summ_invalid(), nb = summ_invalid();
         if (lane < count) {
             h = hyp[node];
-            na = nodeA[node];
-            nb = nodeB[node];
+            const int4 a = nodeA[node], b = nodeB[node];
+            na = {a.x, a.y, a.z, a.w};
+            nb = {b.x, b.y, b.z, b.w};
         }
         s = walk_level(
-            s, count, [&](int E, bool neg) { return pick(E, neg, h, na, nb); },
+            s, count, [&](int E, bool neg) { return pick(E, neg, h.x, h.y, na, nb); },
             [&](int j, float sj) {
-                // open node g0 + j: its 32 tiles
-                const int nd = g0 + j;
-                const int2 hn = hyp[nd];
-                const int4 ta = tileA[(int64_t)nd * 32 + lane], tb = tileB[(int64_t)nd * 32 + lane];
+                // open node g0 + j: every warp prepares one of its tiles under the exact binade of
+                // the state and the neighbouring binade the state is closer to
+                if (lane == 0) {
+                    const int E = exp_field(sj);
+                    sh.e[0] = E;
+                    sh.e[1] = (__float_as_int(sj) & 0x400000) ? E + 1 : E - 1;
+                    sh.cmd = g0 + j;
+                }
+                cta_bar(1);
+                prepare_node(sh, x, n, g0 + j, vec != 0);
+                cta_bar(2);
+                const int e0 = sh.e[0], e1 = sh.e[1];
+                const Summ ta = sh.tile[0][lane], tb = sh.tile[1][lane];
                 return walk_level(
-                    sj, 32, [&](int E, bool neg) { return pick(E, neg, hn, ta, tb); },
+                    sj, 32, [&](int E, bool neg) { return pick(E, neg, e0, e1, ta, tb); },
                     [&](int jt, float st) {
-                        // open tile jt of the node: 32 leaves, summarised under the exact binade
+                        // open tile jt: its 32 leaves, summarised under the exact binade
                         float v[LEAF];
-                        load_leaf(x, n, (int64_t)nd * NODE + (int64_t)jt * TILE, vec != 0, v);
+                        const float4 *src = reinterpret_cast<const float4 *>(&sh.raw[jt][lane * RUN_PITCH]);
+#pragma unroll
+                        for (int i = 0; i < LEAF / 4; i++) {
+                            float4 t = src[i];
+                            v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
+                        }
                         return walk_level(
                             st, 32,
                             [&](int E, bool neg) {
@@ -396,10 +486,12 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
             node_opens);
     }
     if (lane == 0) {
+        sh.cmd = -1;
         out[0] = __fmul_rn(factor, s);
         // how many nodes / tiles / leaves had to be opened (diagnostics, first 16 bytes of scratch)
         stats[0] = node_opens, stats[1] = tile_opens, stats[2] = leaf_opens, stats[3] = nnodes;
     }
+    cta_bar(1);  // releases the helpers
 }
 
 // Short chains: one thread walks shared-memory tiles that the rest of the CTA stages.
@@ -443,22 +535,22 @@ constexpr int64_t kShortChain = 1 << 16;  // below this the plain walk is faster
 
 struct Layout {
     int64_t nnodes;
-    size_t off_stats, off_sum, off_hyp, off_nodeA, off_nodeB, off_tileA, off_tileB, total;
+    size_t off_stats, off_sum, off_hyp, off_nodeA, off_nodeB, total;
 };
 
-Layout layout_for(int64_t n)
+constexpr size_t up256(size_t v) { return (v + 255) & ~(size_t)255; }
+
+constexpr Layout layout_for(int64_t n)
 {
-    Layout L;
+    Layout L{};
     L.nnodes = (n + NODE - 1) / NODE;
-    auto up = [](size_t v) { return (v + 255) & ~(size_t)255; };
+    constexpr auto up = up256;
     size_t o = 0;
     L.off_stats = o; o = up(o + 4 * sizeof(int));
     L.off_sum = o;   o = up(o + (size_t)L.nnodes * sizeof(double));
     L.off_hyp = o;   o = up(o + (size_t)L.nnodes * sizeof(int2));
     L.off_nodeA = o; o = up(o + (size_t)L.nnodes * sizeof(int4));
     L.off_nodeB = o; o = up(o + (size_t)L.nnodes * sizeof(int4));
-    L.off_tileA = o; o = up(o + (size_t)L.nnodes * 32 * sizeof(int4));
-    L.off_tileB = o; o = up(o + (size_t)L.nnodes * 32 * sizeof(int4));
     L.total = o;
     return L;
 }
@@ -481,6 +573,33 @@ extern "C" size_t repdl_b200_sum1d_scratch_bytes(int64_t n)
     return layout_for(n).total;
 }
 
+// The four launches of a long chain on scratch memory `base` (device address, 256-byte aligned,
+// at least layout_for(n).total bytes).  Nothing in the scratch has to be initialised: every word
+// that is read has been written earlier in the same call.
+static int sum1d_long(const float *x, float *out, int64_t n, float factor, char *base, cudaStream_t st)
+{
+    const Layout L = layout_for(n);
+    if (L.nnodes > 0x7FFFFFFF / 32) return REPDL_E_RANGE;
+    double *node_sum = reinterpret_cast<double *>(base + L.off_sum);
+    int2 *hyp = reinterpret_cast<int2 *>(base + L.off_hyp);
+    int4 *nodeA = reinterpret_cast<int4 *>(base + L.off_nodeA);
+    int4 *nodeB = reinterpret_cast<int4 *>(base + L.off_nodeB);
+    const int vec = aligned16(x) ? 1 : 0;
+    const unsigned nn = (unsigned)L.nnodes;
+    int e;
+    node_sum_kernel<<<nn, 256, 0, st>>>(x, n, node_sum, vec);
+    if ((e = launch_status())) return e;
+    node_scan_kernel<<<1, 1024, 0, st>>>(node_sum, (int)nn, hyp);
+    if ((e = launch_status())) return e;
+    summarise_kernel<<<nn, 256, 0, st>>>(x, n, hyp, nodeA, nodeB, vec);
+    if ((e = launch_status())) return e;
+    static unsigned long long smem_done = 0;
+    if ((e = ensure_smem(walk_kernel, WALK_SMEM_BYTES, &smem_done))) return e;
+    walk_kernel<<<1, WALK_THREADS, WALK_SMEM_BYTES, st>>>(x, n, (int)nn, hyp, nodeA, nodeB, factor, out,
+                                                          vec, reinterpret_cast<int *>(base + L.off_stats));
+    return launch_status();
+}
+
 extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float factor, void *scratch,
                                 size_t scratch_bytes, void *stream)
 {
@@ -489,27 +608,8 @@ extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float fac
     if (!out || (n > 0 && !x)) return REPDL_E_NULL;
     cudaStream_t st = (cudaStream_t)stream;
     if (n < kShortChain) return sum1d_plain(x, out, n, factor, st);
-    const Layout L = layout_for(n);
-    if (L.nnodes > 0x7FFFFFFF / 32) return REPDL_E_RANGE;
-    if (!scratch || scratch_bytes < L.total || (reinterpret_cast<uintptr_t>(scratch) & 255u))
+    if (!scratch || scratch_bytes < layout_for(n).total ||
+        (reinterpret_cast<uintptr_t>(scratch) & 255u))
         return REPDL_E_SCRATCH;
-    char *base = static_cast<char *>(scratch);
-    double *node_sum = reinterpret_cast<double *>(base + L.off_sum);
-    int2 *hyp = reinterpret_cast<int2 *>(base + L.off_hyp);
-    int4 *nodeA = reinterpret_cast<int4 *>(base + L.off_nodeA);
-    int4 *nodeB = reinterpret_cast<int4 *>(base + L.off_nodeB);
-    int4 *tileA = reinterpret_cast<int4 *>(base + L.off_tileA);
-    int4 *tileB = reinterpret_cast<int4 *>(base + L.off_tileB);
-    const int vec = aligned16(x) ? 1 : 0;
-    const unsigned nn = (unsigned)L.nnodes;
-    int e;
-    node_sum_kernel<<<nn, 256, 0, st>>>(x, n, node_sum, vec);
-    if ((e = launch_status())) return e;
-    node_scan_kernel<<<1, 1024, 0, st>>>(node_sum, (int)nn, hyp);
-    if ((e = launch_status())) return e;
-    summarise_kernel<<<nn, 256, 0, st>>>(x, n, hyp, tileA, tileB, nodeA, nodeB, vec);
-    if ((e = launch_status())) return e;
-    walk_kernel<<<1, 32, 0, st>>>(x, n, (int)nn, hyp, tileA, tileB, nodeA, nodeB, factor, out, vec,
-                                  reinterpret_cast<int *>(base + L.off_stats));
-    return launch_status();
+    return sum1d_long(x, out, n, factor, static_cast<char *>(scratch), st);
 }

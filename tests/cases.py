@@ -130,6 +130,8 @@ def build_cases():
                 x = torch.randn(n, generator=g) * torch.exp2(torch.randint(-30, 30, (n,), generator=g).float())
             elif dist == "tiny":        # mostly absorbed
                 x = torch.randn(n, generator=g) * 1e-3
+            elif dist == "pos":         # one sign only: the chain saturates at a power of two
+                x = torch.rand(n, generator=g) * scale
             if first is not None:
                 x[0] = first
             return (x, False)
@@ -143,6 +145,12 @@ def build_cases():
     cases.append(("sum1d_long_wide", "sum1d", mk_long(736, 400000, 1.0, dist="wide")))
     cases.append(("sum1d_long_absorbed", "sum1d", mk_long(737, 700000, 1.0, first=4.0e6, dist="tiny")))
     cases.append(("sum1d_long_signflips", "sum1d", mk_long(738, 300000, 1.0e-3)))
+
+    cases.append(("sum1d_long_saturate_pos", "sum1d", mk_long(742, 400000, 1.0, first=16700000.0, dist="pos")))
+    cases.append(("sum1d_long_saturate_neg", "sum1d", mk_long(743, 400000, -1.0, first=-16700000.0, dist="pos")))
+    cases.append(("sum1d_long_boundary_neg", "sum1d", mk_long(744, 500000, 0.05, first=-1048576.0)))
+    cases.append(("sum1d_long_boundary_pos", "sum1d", mk_long(745, 500000, 0.05, first=2097152.0)))
+    cases.append(("sum1d_long_lognormal_neg", "sum1d", mk_long(746, 1 << 20, 1.0, first=-1048000.0, dist="lognormal")))
 
     def mk_long_cancel():
         x = _randn(739, 400000, scale=1e6)
