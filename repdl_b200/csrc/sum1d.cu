@@ -91,8 +91,9 @@ __device__ __forceinline__ Summ shfl_up_summ(const Summ &s, int delta)
 
 // Summary of the elements v[0..LEAF) (in order) under binade hypothesis E (exponent field).
 // Hypotheses outside [24, 253] are not summarised (the scale 2^(150-E) must be a finite float).
-__device__ __forceinline__ Summ leaf_summary(const float (&v)[LEAF], int E)
+__device__ __forceinline__ Summ leaf_summary(const float (&v)[LEAF], int E, bool *had_tie = nullptr)
 {
+    if (had_tie) *had_tie = false;
     if (E < 24 || E > 253) return summ_invalid();
     const float scale = __int_as_float((277 - E) << 23);  // 2^(150 - E)
     const float MAGIC = 12582912.0f;                       // 1.5 * 2^23: q + MAGIC rounds q to an integer
@@ -125,6 +126,7 @@ __device__ __forceinline__ Summ leaf_summary(const float (&v)[LEAF], int E)
         }
         d0 += R;
     }
+    if (had_tie) *had_tie = tie_seen;
     if (bad) return summ_invalid();
     // after a tie the odd-parity track may run one off the even one: widen by 1 to cover both
     const int margin = tie_seen ? 1 : 0;
@@ -141,73 +143,253 @@ __device__ __forceinline__ float apply_inc(float s, int inc)
     return __int_as_float((int)((b & 0xFF800000u) | ((unsigned)m & 0x7FFFFFu)));
 }
 
-// One level of the walk, run by one full warp.  `count` children (<= 32), child c owned by lane c.
-//   get(E, negative) -> this lane's summary for a state in binade E (already negated for s < 0),
-//                       or an invalid summary;
-//   open(j, s)       -> the exact state after child j entered with state s (warp-uniform call).
-// Returns the exact state after all children.
-template <class Get, class Open>
-__device__ __forceinline__ float walk_level(float s, int count, Get get, Open open, int &opens)
+// Scan context of one binade hypothesis over the 32 children of a level (one child per lane).
+struct Ctx {
+    Summ mine;   // this lane's child under binade E (positive orientation; identity before pos0)
+    int c0, c1;  // increments of |m| from pos0 to this lane's start, for even / odd m at pos0
+    int t0, t1;  // the same through the last child
+    unsigned tiemask, invmask;
+    int E, pos0;
+};
+
+__device__ __forceinline__ void ctx_scan(Ctx &cx, int pos)
 {
     const int lane = threadIdx.x & 31;
+    if (lane < pos) cx.mine = summ_identity();
+    Summ incl = cx.mine;
+#pragma unroll
+    for (int dlt = 1; dlt < 32; dlt <<= 1) {
+        Summ up = shfl_up_summ(incl, dlt);
+        if (lane >= dlt) incl = summ_compose(up, incl);
+    }
+    cx.c0 = __shfl_up_sync(0xffffffffu, incl.d0, 1);
+    cx.c1 = __shfl_up_sync(0xffffffffu, incl.d1, 1);
+    if (lane <= pos) cx.c0 = cx.c1 = 0;
+    cx.t0 = __shfl_sync(0xffffffffu, incl.d0, 31);
+    cx.t1 = __shfl_sync(0xffffffffu, incl.d1, 31);
+    cx.tiemask = __ballot_sync(0xffffffffu, lane >= pos && cx.mine.d0 != cx.mine.d1);
+    cx.invmask = __ballot_sync(0xffffffffu, lane >= pos && summ_is_invalid(cx.mine));
+    cx.pos0 = pos;
+}
+
+// One level of the walk, run by one full warp.  `count` children (<= 32), child c owned by lane c
+// (lanes >= count must supply identity summaries).
+//   hypE0/hypE1      the two binades for which summaries exist up front;
+//   getH(k)          this lane's summary under hypothesis k (positive orientation);
+//   getE(E)          this lane's summary under an arbitrary binade E, or invalid if the level
+//                    cannot make one;
+//   open(j, s)       the exact state after child j entered with state s (warp-uniform call).
+// Returns the exact state after all children.  The two contexts are scanned once; after an opened
+// child the prefix increments of the context that matches the new binade are re-anchored on the
+// new exact state, which is valid while no child with an invalid summary has been passed and --
+// where ties follow -- a start parity exists that reproduces the actual parity.
+template <class GetH, class GetE, class Open>
+__device__ __forceinline__ float walk_level(float s, int count, int hypE0, int hypE1, GetH getH,
+                                            GetE getE, Open open, int &opens)
+{
+    const int lane = threadIdx.x & 31;
+    Ctx cxA, cxB;  // kept as two named objects so that they stay in registers
+    cxA.mine = lane < count ? getH(0) : summ_identity();
+    cxA.E = hypE0;
+    ctx_scan(cxA, 0);
+    cxB.mine = lane < count ? getH(1) : summ_identity();
+    cxB.E = hypE1;
+    ctx_scan(cxB, 0);
     int pos = 0;
-    // context of the last scan: summaries, assumed cumulative increment c (from pos0 to this lane's
-    // start, for start parity par0), start state m0
-    Summ mine = summ_identity(), incl = summ_identity();
-    int c = 0, m0 = 0, pos0 = 0, scanE = -1;
-    bool scanNeg = false, have = false;
-    unsigned tiemask = 0, invmask = 0;
-    while (pos < count) {
-        const int E = exp_field(s);
+    bool done = false;
+    // one attempt to advance with context c (which matches the binade of s); opens one child
+    auto step = [&](Ctx &c) {
         const bool neg = __float_as_int(s) < 0;
         const int m = (int)(((unsigned)__float_as_int(s) & 0x7FFFFFu) | 0x800000u);
         const unsigned from_pos = 0xFFFFFFFFu << pos;
-        bool reuse = have && E == scanE && neg == scanNeg &&
-                     (invmask & (0xFFFFFFFFu << pos0) & ~from_pos) == 0u;
-        int delta = 0;
-        if (reuse) {
-            const int a_pos = m0 + __shfl_sync(0xffffffffu, c, pos);
-            // a different parity changes the outcome of later ties
-            if (((m ^ a_pos) & 1) && (tiemask & from_pos)) reuse = false;
-            delta = m - a_pos;
+        // pick the start parity p whose track has the actual parity at pos
+        int p = -1;
+        if ((c.invmask & (0xFFFFFFFFu << c.pos0) & ~from_pos) == 0u) {
+            const int a0 = __shfl_sync(0xffffffffu, c.c0, pos), a1 = __shfl_sync(0xffffffffu, c.c1, pos);
+            if (((a0 ^ m) & 1) == 0)
+                p = 0;
+            else if ((((1 + a1) ^ m) & 1) == 0)
+                p = 1;
+            else if ((c.tiemask & from_pos) == 0u)
+                p = 0;  // no tie ahead: the increments do not depend on parity
         }
-        if (!reuse) {
-            const bool active = lane >= pos && lane < count;
-            mine = active ? ((E < 24 || E > 253) ? summ_invalid() : get(E, neg)) : summ_identity();
-            incl = mine;
-#pragma unroll
-            for (int dlt = 1; dlt < 32; dlt <<= 1) {
-                Summ up = shfl_up_summ(incl, dlt);
-                if (lane >= dlt) incl = summ_compose(up, incl);
-            }
-            const int par0 = m & 1;
-            const int incd = par0 ? incl.d1 : incl.d0;
-            c = __shfl_up_sync(0xffffffffu, incd, 1);
-            if (lane <= pos) c = 0;
-            m0 = m, pos0 = pos, scanE = E, scanNeg = neg, have = true, delta = 0;
-            tiemask = __ballot_sync(0xffffffffu, active && mine.d0 != mine.d1);
-            invmask = __ballot_sync(0xffffffffu, active && summ_is_invalid(mine));
+        if (p < 0) {
+            ctx_scan(c, pos);
+            p = m & 1;
         }
-        // lanes after an invalid lane carry a meaningless c; they are never reached before a rescan
-        const int m_in = m0 + c + delta;
+        const int cl = p ? c.c1 : c.c0;
+        const int cpos = __shfl_sync(0xffffffffu, cl, pos);
+        const int m_in = m + (neg ? -(cl - cpos) : (cl - cpos));  // |m| entering this lane's child
+        const int wlo = neg ? -c.mine.hi : c.mine.lo, whi = neg ? -c.mine.lo : c.mine.hi;
         bool ok = true;
         if (lane >= pos && lane < count) {
-            ok = !summ_is_invalid(mine) && ((invmask & (0xFFFFFFFFu << pos0) & ~(0xFFFFFFFFu << lane)) == 0u) &&
-                 (m_in + mine.lo >= M_LO) && (m_in + mine.hi < M_HI);
+            ok = !summ_is_invalid(c.mine) &&
+                 ((c.invmask & (0xFFFFFFFFu << c.pos0) & ~(0xFFFFFFFFu << lane)) == 0u) &&
+                 (m_in + wlo >= M_LO) && (m_in + whi < M_HI);
         }
         const unsigned badmask = __ballot_sync(0xffffffffu, !ok);
         if (badmask == 0u) {
-            // all remaining children valid: total increment = prefix through the last lane
-            const int par0 = m0 & 1;
-            const int tot = __shfl_sync(0xffffffffu, par0 ? incl.d1 : incl.d0, 31);
-            return apply_inc(s, (m0 + tot + delta) - m);
+            const int tot = (p ? c.t1 : c.t0) - cpos;
+            s = apply_inc(s, neg ? -tot : tot);
+            done = true;
+            return;
         }
         const int j = __ffs((int)badmask) - 1;
         if (j > pos) s = apply_inc(s, __shfl_sync(0xffffffffu, m_in, j) - m);
         s = open(j, s);
         opens++;
         pos = j + 1;
+    };
+    while (pos < count && !done) {
+        const int E = exp_field(s);
+        if (E == cxA.E) {
+            step(cxA);
+        } else {
+            if (E != cxB.E) {
+                // a binade nobody prepared: make a context for it in slot B, from pos on
+                cxB.mine = (lane >= pos && lane < count)
+                               ? ((E < 24 || E > 253) ? summ_invalid() : getE(E))
+                               : summ_identity();
+                cxB.E = E;
+                ctx_scan(cxB, pos);
+            }
+            step(cxB);
+        }
     }
+    return s;
+}
+
+// ------------------------------------------------------------------------------------------------
+// The leaf level of the walk uses a lighter algebra: a leaf that contains an exact tie is simply
+// treated like an invalid one (it is walked with real adds), so a leaf is (d, lo, hi) with no
+// parity tracks and composition is an add and two min/max.  Ties are rare (about 1 step in 10^4),
+// and only leaves of opened tiles pass through here, so this costs a handful of extra leaf walks.
+// ------------------------------------------------------------------------------------------------
+// Cycle counters of the walker warp, kept in the scratch header for diagnostics.
+struct WalkClock {
+    long long prepare, tile_scan, leaf_steps, raw, rebuild, load;
+};
+
+struct LeafCtx {
+    int lo, hi;   // this lane's leaf: extreme (increment so far + floor/ceil(q)), relative to its start
+    int c, tot;   // increment from pos0 to this lane's start / through the last leaf
+    unsigned invmask;
+    int E, pos0;
+};
+
+__device__ __forceinline__ void leaf_ctx_build(LeafCtx &cx, const float (&v)[LEAF], int E, int pos)
+{
+    const int lane = threadIdx.x & 31;
+    const bool usable = E >= 24 && E <= 253;
+    const float scale = __int_as_float((277 - (usable ? E : 127)) << 23);  // 2^(150 - E)
+    const float MAGIC = 12582912.0f;
+    int d = 0, lo = BIGI, hi = -BIGI;
+    bool bad = !usable;
+#pragma unroll
+    for (int i = 0; i < LEAF; i++) {
+        const float q = __fmul_rn(v[i], scale);
+        const float t = __fadd_rn(q, MAGIC);
+        const int R = __float_as_int(t) - 0x4B400000;
+        const float r = __fsub_rn(q, __fsub_rn(t, MAGIC));       // q - rint(q)
+        bad |= !(fabsf(q) < 4194304.0f) | (fabsf(r) == 0.5f);     // huge, inf, NaN or an exact tie
+        const int fl = d + R + (__float_as_int(r) >> 31);
+        lo = min(lo, fl);
+        hi = max(hi, fl + (r != 0.0f ? 1 : 0));
+        d += R;
+    }
+    if (lane < pos) d = 0, lo = BIGI, hi = -BIGI, bad = false;
+    cx.lo = lo, cx.hi = hi;
+    cx.invmask = __ballot_sync(0xffffffffu, bad);
+    // inclusive prefix sum of d (values past an invalid leaf are never used before a rebuild)
+    int incl = bad ? 0 : d;
+#pragma unroll
+    for (int dlt = 1; dlt < 32; dlt <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, dlt);
+        if (lane >= dlt) incl += up;
+    }
+    cx.c = __shfl_up_sync(0xffffffffu, incl, 1);
+    if (lane == 0) cx.c = 0;
+    cx.tot = __shfl_sync(0xffffffffu, incl, 31);
+    cx.E = E, cx.pos0 = pos;
+}
+
+// The same context made from a full leaf summary that is already at hand (whole tile, pos = 0).
+__device__ __forceinline__ void leaf_ctx_from_summary(LeafCtx &cx, const Summ &sm, bool tie, int E)
+{
+    const int lane = threadIdx.x & 31;
+    const bool bad = tie || summ_is_invalid(sm);
+    cx.lo = sm.lo, cx.hi = sm.hi;
+    cx.invmask = __ballot_sync(0xffffffffu, bad);
+    int incl = bad ? 0 : sm.d0;
+#pragma unroll
+    for (int dlt = 1; dlt < 32; dlt <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, incl, dlt);
+        if (lane >= dlt) incl += up;
+    }
+    cx.c = __shfl_up_sync(0xffffffffu, incl, 1);
+    if (lane == 0) cx.c = 0;
+    cx.tot = __shfl_sync(0xffffffffu, incl, 31);
+    cx.E = E, cx.pos0 = 0;
+}
+
+// Walks the 32 leaves (lane-owned runs v) of one tile from exact state s, starting from the two
+// prepared contexts.
+__device__ __forceinline__ float walk_leaves(float s, const float (&v)[LEAF], LeafCtx cxA, LeafCtx cxB,
+                                             int &opens, WalkClock &clk)
+{
+    const int lane = threadIdx.x & 31;
+    const long long t_enter = clock64();
+    int pos = 0;
+    bool done = false;
+    auto step = [&](LeafCtx &c) {
+        const bool neg = __float_as_int(s) < 0;
+        const int m = (int)(((unsigned)__float_as_int(s) & 0x7FFFFFu) | 0x800000u);
+        // c.c is a plain prefix sum in which an invalid leaf counts as 0, so the difference
+        // c.c - cpos is exact for every lane with no invalid leaf in [pos, lane): invalid leaves
+        // that have already been passed cancel out and never force a rebuild
+        const int cpos = __shfl_sync(0xffffffffu, c.c, pos);
+        const int m_in = m + (neg ? -(c.c - cpos) : (c.c - cpos));
+        const int wlo = neg ? -c.hi : c.lo, whi = neg ? -c.lo : c.hi;
+        const unsigned inv_ahead = c.invmask & (0xFFFFFFFFu << pos);
+        const bool before_inv = (inv_ahead & ~(0xFFFFFFFFu << lane)) != 0u;
+        const bool ok = lane < pos || lane < c.pos0 ||
+                        (!((c.invmask >> lane) & 1u) && !before_inv && (m_in + wlo >= M_LO) &&
+                         (m_in + whi < M_HI));
+        const unsigned badmask = __ballot_sync(0xffffffffu, !ok);
+        if (badmask == 0u) {
+            const int tot = c.tot - cpos;
+            s = apply_inc(s, neg ? -tot : tot);
+            done = true;
+            return;
+        }
+        const int j = __ffs((int)badmask) - 1;
+        if (j > pos) s = apply_inc(s, __shfl_sync(0xffffffffu, m_in, j) - m);
+        // open leaf j: 32 real fp32 adds by its owner
+        const long long t0 = clock64();
+        float r = s;
+        if (lane == j) {
+#pragma unroll
+            for (int i = 0; i < LEAF; i++) r = __fadd_rn(r, v[i]);
+        }
+        s = __shfl_sync(0xffffffffu, r, j);
+        clk.raw += clock64() - t0;
+        opens++;
+        pos = j + 1;
+    };
+    while (pos < 32 && !done) {
+        const int E = exp_field(s);
+        if (E == cxA.E) {
+            step(cxA);
+        } else {
+            if (E != cxB.E) {
+                const long long t0 = clock64();
+                leaf_ctx_build(cxB, v, E, pos);
+                clk.rebuild += clock64() - t0;
+            }
+            step(cxB);
+        }
+    }
+    clk.leaf_steps += clock64() - t_enter;
     return s;
 }
 
@@ -355,23 +537,14 @@ summarise_kernel(const float *__restrict__ x, int64_t n, const int2 *__restrict_
 // ---------------------------------------------------------------------------------------------
 // 4. the walk: one CTA; warp 0 walks, all warps prepare an opened node
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ Summ pick(int E, bool neg, int e0, int e1, const Summ &a, const Summ &b)
-{
-    Summ s;
-    if (E == e0)
-        s = a;
-    else if (E == e1)
-        s = b;
-    else
-        return summ_invalid();
-    return neg ? summ_negate(s) : s;
-}
-
 constexpr int WALK_THREADS = 512;   // 16 warps: each prepares two tiles of an opened node
 constexpr int RUN_PITCH = 36;  // floats per lane-run in shared memory: LDS.128 without bank conflicts
 struct WalkShared {
     float raw[32][32 * RUN_PITCH];  // the 32 tiles of the opened node
     Summ tile[2][32];               // tile summaries under the two binades of `e`
+    int leaf_lo[2][32][32], leaf_hi[2][32][32], leaf_c[2][32][32];  // leaf contexts, [binade][tile][lane]
+    int leaf_tot[2][32];
+    unsigned leaf_inv[2][32];
     int e[2];
     int cmd;                        // node to open, or -1: finished
 };
@@ -394,11 +567,21 @@ __device__ __forceinline__ void prepare_node(WalkShared &sh, const float *__rest
 #pragma unroll
         for (int i = 0; i < LEAF / 4; i++)
             dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-        Summ a = warp_reduce_summ(leaf_summary(v, sh.e[0]));
-        Summ b = warp_reduce_summ(leaf_summary(v, sh.e[1]));
-        if (lane == 0) {
-            sh.tile[0][tl] = a;
-            sh.tile[1][tl] = b;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            bool tie;
+            const Summ leaf = leaf_summary(v, sh.e[h], &tie);
+            LeafCtx cx;
+            leaf_ctx_from_summary(cx, leaf, tie, sh.e[h]);
+            sh.leaf_lo[h][tl][lane] = cx.lo;
+            sh.leaf_hi[h][tl][lane] = cx.hi;
+            sh.leaf_c[h][tl][lane] = cx.c;
+            const Summ t = warp_reduce_summ(leaf);
+            if (lane == 0) {
+                sh.tile[h][tl] = t;
+                sh.leaf_tot[h][tl] = cx.tot;
+                sh.leaf_inv[h][tl] = cx.invmask;
+            }
         }
     }
 }
@@ -426,6 +609,8 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
 
     float s = 0.0f;
     int node_opens = 0, tile_opens = 0, leaf_opens = 0;
+    WalkClock clk = {0, 0, 0, 0, 0, 0};
+    const long long t_begin = clock64();
     for (int g0 = 0; g0 < nnodes; g0 += 32) {
         const int count = min(32, nnodes - g0);
         const int node = g0 + lane;
@@ -437,26 +622,39 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
             na = {a.x, a.y, a.z, a.w};
             nb = {b.x, b.y, b.z, b.w};
         }
+        // both hypotheses of a group's nodes may differ from node to node; the level works with two
+        // binades, so take those of the group's first node and let other nodes report "invalid"
+        const int gE0 = __shfl_sync(0xffffffffu, h.x, 0), gE1 = __shfl_sync(0xffffffffu, h.y, 0);
+        auto node_summ = [&](int E) {
+            if (E == h.x) return na;
+            if (E == h.y) return nb;
+            return summ_invalid();
+        };
         s = walk_level(
-            s, count, [&](int E, bool neg) { return pick(E, neg, h.x, h.y, na, nb); },
+            s, count, gE0, gE1, [&](int k) { return node_summ(k ? gE1 : gE0); },
+            [&](int E) { return node_summ(E); },
             [&](int j, float sj) {
-                // open node g0 + j: every warp prepares one of its tiles under the exact binade of
-                // the state and the neighbouring binade the state is closer to
+                // open node g0 + j: every warp prepares tiles of it under the exact binade of the
+                // state and the neighbouring binade the state is closer to
                 if (lane == 0) {
                     const int E = exp_field(sj);
                     sh.e[0] = E;
                     sh.e[1] = (__float_as_int(sj) & 0x400000) ? E + 1 : E - 1;
                     sh.cmd = g0 + j;
                 }
+                const long long tp = clock64();
                 cta_bar(1);
                 prepare_node(sh, x, n, g0 + j, vec != 0);
                 cta_bar(2);
+                clk.prepare += clock64() - tp;
                 const int e0 = sh.e[0], e1 = sh.e[1];
                 const Summ ta = sh.tile[0][lane], tb = sh.tile[1][lane];
                 return walk_level(
-                    sj, 32, [&](int E, bool neg) { return pick(E, neg, e0, e1, ta, tb); },
+                    sj, 32, e0, e1, [&](int k) { return k ? tb : ta; },
+                    [&](int) { return summ_invalid(); },
                     [&](int jt, float st) {
-                        // open tile jt: its 32 leaves, summarised under the exact binade
+                        // open tile jt: its 32 leaves, summarised under the same two binades
+                        const long long tl0 = clock64();
                         float v[LEAF];
                         const float4 *src = reinterpret_cast<const float4 *>(&sh.raw[jt][lane * RUN_PITCH]);
 #pragma unroll
@@ -464,22 +662,15 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
                             float4 t = src[i];
                             v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
                         }
-                        return walk_level(
-                            st, 32,
-                            [&](int E, bool neg) {
-                                Summ q = leaf_summary(v, E);
-                                return neg ? summ_negate(q) : q;
-                            },
-                            [&](int jl, float sl) {
-                                // open leaf jl: 32 real fp32 adds by its owner
-                                float r = sl;
-                                if (lane == jl) {
-#pragma unroll
-                                    for (int i = 0; i < LEAF; i++) r = __fadd_rn(r, v[i]);
-                                }
-                                return __shfl_sync(0xffffffffu, r, jl);
-                            },
-                            leaf_opens);
+                        LeafCtx ca, cb;
+                        ca.lo = sh.leaf_lo[0][jt][lane], ca.hi = sh.leaf_hi[0][jt][lane];
+                        ca.c = sh.leaf_c[0][jt][lane], ca.tot = sh.leaf_tot[0][jt];
+                        ca.invmask = sh.leaf_inv[0][jt], ca.E = e0, ca.pos0 = 0;
+                        cb.lo = sh.leaf_lo[1][jt][lane], cb.hi = sh.leaf_hi[1][jt][lane];
+                        cb.c = sh.leaf_c[1][jt][lane], cb.tot = sh.leaf_tot[1][jt];
+                        cb.invmask = sh.leaf_inv[1][jt], cb.E = e1, cb.pos0 = 0;
+                        clk.load += clock64() - tl0;
+                        return walk_leaves(st, v, ca, cb, leaf_opens, clk);
                     },
                     tile_opens);
             },
@@ -490,6 +681,9 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
         out[0] = __fmul_rn(factor, s);
         // how many nodes / tiles / leaves had to be opened (diagnostics, first 16 bytes of scratch)
         stats[0] = node_opens, stats[1] = tile_opens, stats[2] = leaf_opens, stats[3] = nnodes;
+        long long *cl = reinterpret_cast<long long *>(stats + 4);
+        cl[0] = clock64() - t_begin, cl[1] = clk.prepare, cl[2] = clk.leaf_steps, cl[3] = clk.raw;
+        cl[4] = clk.rebuild, cl[5] = clk.load;
     }
     cta_bar(1);  // releases the helpers
 }
@@ -546,7 +740,7 @@ constexpr Layout layout_for(int64_t n)
     L.nnodes = (n + NODE - 1) / NODE;
     constexpr auto up = up256;
     size_t o = 0;
-    L.off_stats = o; o = up(o + 4 * sizeof(int));
+    L.off_stats = o; o = up(o + 4 * sizeof(int) + 8 * sizeof(long long));
     L.off_sum = o;   o = up(o + (size_t)L.nnodes * sizeof(double));
     L.off_hyp = o;   o = up(o + (size_t)L.nnodes * sizeof(int2));
     L.off_nodeA = o; o = up(o + (size_t)L.nnodes * sizeof(int4));
