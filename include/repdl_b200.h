@@ -34,6 +34,7 @@ extern "C" {
 #define REPDL_E_RANGE (-3)     /* a size exceeds what the kernel indexes (see each call) */
 #define REPDL_E_SCRATCH (-4)   /* scratch buffer missing or too small */
 #define REPDL_E_UNSUPPORTED (-5)
+#define REPDL_E_STATIC_MAX (-6) /* input larger than a built-in (static) scratch array supports */
 
 /* Library version and the compute capability the kernels were compiled for (100). */
 int repdl_b200_version(void);
@@ -94,6 +95,23 @@ int repdl_b200_conv2d_grad_kernel(const float *grad_output, const float *input,
 size_t repdl_b200_sum1d_scratch_bytes(int64_t n);
 int repdl_b200_sum1d(const float *x, float *out, int64_t n, float factor, void *scratch,
                      size_t scratch_bytes, void *stream);
+/* The same chain sum for callers that cannot allocate device memory at all.  (No counterpart in
+ * the reference.)  Some hosts of this library are not allowed to call cudaMalloc or to go through
+ * an allocating framework on the path that needs the sum: code running inside a CUDA-graph capture,
+ * real-time or interrupt-like callbacks, a process whose memory pool is owned and fully handed out
+ * by someone else, or a plugin ABI that only passes inputs and outputs.  For them the scratch of
+ * repdl_b200_sum1d lives in a fixed array inside this library's device image (about 1.5 MB, held by
+ * every GPU that loads the library until the process exits), so the caller passes only x and out.
+ *   - n may be at most repdl_b200_sum1d_static_max_n() (2^30 elements); a longer chain returns
+ *     REPDL_E_STATIC_MAX and does nothing.
+ *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
+ *     that device current).  Make that first call before starting any stream capture.
+ *   - Every call on a device shares the one array and it keeps the previous call's contents.
+ *     Nothing in it has to be cleared (each call writes every word before reading it), but two calls
+ *     whose kernels can overlap on the GPU (different streams) race on it: serialise them.
+ *   - No cudaMalloc, cudaFree or other allocating call is made, on any call. */
+int64_t repdl_b200_sum1d_static_max_n(void);
+int repdl_b200_sum1d_static(const float *x, float *out, int64_t n, float factor, void *stream);
 /* out[j] = factor * chain over i of x[i*N + j]   (M rows, N columns) */
 int repdl_b200_sum2d_dim0(const float *x, float *out, int64_t M, int64_t N, float factor,
                           void *stream);

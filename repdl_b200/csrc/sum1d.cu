@@ -807,3 +807,48 @@ extern "C" int repdl_b200_sum1d(const float *x, float *out, int64_t n, float fac
         return REPDL_E_SCRATCH;
     return sum1d_long(x, out, n, factor, static_cast<char *>(scratch), st);
 }
+
+// ------------------------------------------------------------------------------------------------
+// The same chain sum for callers that must not allocate: the scratch is a fixed array in this
+// library's device image instead of a buffer the caller provides.
+// ------------------------------------------------------------------------------------------------
+namespace {
+constexpr int64_t kStaticMaxN = (int64_t)1 << 30;                    // 2^30 elements (4 GiB of input)
+constexpr size_t kStaticScratchBytes = layout_for(kStaticMaxN).total;  // about 1.5 MB
+constexpr int kMaxDevices = 64;
+}  // namespace
+
+// Lives in the device image of every GPU that loads this library, for the life of the process.
+static __device__ __align__(256) unsigned char g_sum1d_static_scratch[kStaticScratchBytes];
+
+// In host code `g_sum1d_static_scratch` is only a handle for the symbol, not something a kernel can
+// dereference; the address the kernels need is asked for once per device, with that device current.
+static void *g_static_scratch_addr[kMaxDevices];
+
+extern "C" int64_t repdl_b200_sum1d_static_max_n(void) { return kStaticMaxN; }
+
+extern "C" int repdl_b200_sum1d_static(const float *x, float *out, int64_t n, float factor,
+                                       void *stream)
+{
+    clear_stale_error();
+    if (n < 0) return REPDL_E_SHAPE;
+    if (n > kStaticMaxN) return REPDL_E_STATIC_MAX;  // the built-in scratch is sized for kStaticMaxN elements
+    if (!out || (n > 0 && !x)) return REPDL_E_NULL;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (n < kShortChain) return sum1d_plain(x, out, n, factor, st);
+    int dev = 0;
+    cudaError_t ce = cudaGetDevice(&dev);
+    if (ce != cudaSuccess) return (int)ce;
+    if (dev < 0 || dev >= kMaxDevices) return REPDL_E_RANGE;
+    void *addr = __atomic_load_n(&g_static_scratch_addr[dev], __ATOMIC_ACQUIRE);
+    if (!addr) {
+        // first call on this device: resolve the symbol's device address (no allocation happens;
+        // two threads racing here obtain the same address)
+        ce = cudaGetSymbolAddress(&addr, g_sum1d_static_scratch);
+        if (ce != cudaSuccess) return (int)ce;
+        if (!addr) return REPDL_E_SCRATCH;
+        __atomic_store_n(&g_static_scratch_addr[dev], addr, __ATOMIC_RELEASE);
+    }
+    // nothing in the scratch needs clearing: each call writes every word before reading it
+    return sum1d_long(x, out, n, factor, static_cast<char *>(addr), st);
+}
