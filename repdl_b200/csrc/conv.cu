@@ -5,9 +5,20 @@
 // loop order; taps that fall into the padding are SKIPPED (not multiplied by zero -- a zero
 // product would turn an accumulator of -0 into +0 and a non-finite weight into NaN).
 //
-// The kernels in this file are the direct form: one thread owns one output element and walks its
-// chain exactly as the reference's loops do.  Threads of a warp own adjacent output elements, so
-// the loads of one tap are coalesced along the innermost dimension.
+// Two forms live in this file.
+//   direct : one thread owns one output element and walks its chain exactly as the reference's
+//            loops do (always exact; used for conv2d_grad_kernel, for kernels with more than 64
+//            taps and as the per-tile fallback of the other form);
+//   GEMM   : conv2d and conv2d_grad_input as an implicit GEMM on the FP32 FMA pipe -- the same
+//            register-blocked main loop as mm (8 x 8 outputs per thread, K in slabs of 16 through
+//            double-buffered shared memory), with the im2col matrix gathered on the fly.  A tap that
+//            falls into the padding enters the FMA as +0.0 instead of being skipped.  That is the
+//            identity for every accumulator except -0, and an accumulator that started at +0 can
+//            only become -0 when a non-zero product underflows to zero; so each CTA watches its
+//            operands while loading them and, if it meets a non-finite value or a non-zero value
+//            below 2^-74 (products of larger values cannot underflow to zero), discards its tile
+//            and recomputes it with the direct form.  Wrong bits are therefore impossible, not
+//            merely unlikely.
 #include "common.cuh"
 
 namespace repdl_b200 {
@@ -15,7 +26,14 @@ namespace {
 
 struct ConvDims {
     int N, IC, H, W, OC, KH, KW, OH, OW, sH, sW, pH, pW, groups;
+    unsigned long long m40_khw, m40_kw, m40_ow;  // ceil(2^40 / (KH*KW)), / KW, / OW: division by multiplication
 };
+
+// k / dv with m40 = ceil(2^40 / dv): exact whenever k * dv < 2^40 (callers keep k < 2^24, dv < 2^16).
+__device__ __forceinline__ int fastdiv(int k, unsigned long long m40)
+{
+    return (int)(((unsigned long long)(unsigned)k * m40) >> 40);
+}
 
 constexpr int CONV_THREADS = 128;
 
@@ -122,6 +140,442 @@ conv2d_grad_kernel_direct_kernel(const float *__restrict__ GO, const float *__re
     GK[idx] = acc;
 }
 
+// ------------------------------------------------------------------------------------------------
+// exact per-element chains as device functions (the fallback of the GEMM form)
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float conv2d_exact(const float *__restrict__ I, const float *__restrict__ Kw,
+                                              const ConvDims &d, int n, int oc, int oh, int ow)
+{
+    const int ICg = d.IC / d.groups, OCg = d.OC / d.groups;
+    const int g = oc / OCg;
+    const int h0 = oh * d.sH - d.pH, w0 = ow * d.sW - d.pW;
+    const float *ip = I + ((int64_t)n * d.IC + (int64_t)g * ICg) * d.H * d.W;
+    const float *kp = Kw + (int64_t)oc * ICg * d.KH * d.KW;
+    float acc = 0.0f;
+    for (int i = 0; i < ICg; i++)
+        for (int kh = 0; kh < d.KH; kh++) {
+            int h = h0 + kh;
+            if (h < 0 || h >= d.H) continue;
+            for (int kw = 0; kw < d.KW; kw++) {
+                int w = w0 + kw;
+                if (w < 0 || w >= d.W) continue;
+                acc = __fmaf_rn(__ldg(ip + ((int64_t)i * d.H + h) * d.W + w),
+                                __ldg(kp + (i * d.KH + kh) * d.KW + kw), acc);
+            }
+        }
+    return acc;
+}
+
+__device__ __forceinline__ float conv2d_grad_input_exact(const float *__restrict__ GO,
+                                                         const float *__restrict__ Kw,
+                                                         const ConvDims &d, int n, int ic, int h, int w)
+{
+    const float *gp = GO + (int64_t)n * d.OC * d.OH * d.OW;
+    float acc = 0.0f;
+    for (int oc = 0; oc < d.OC; oc++) {
+        const float *kp = Kw + ((int64_t)oc * d.IC + ic) * d.KH * d.KW;
+        for (int kh = 0; kh < d.KH; kh++) {
+            int nh = h - kh + d.pH;
+            if (nh < 0) continue;
+            int oh = nh / d.sH;
+            if (oh >= d.OH || oh * d.sH != nh) continue;
+            for (int kw = 0; kw < d.KW; kw++) {
+                int nw = w - kw + d.pW;
+                if (nw < 0) continue;
+                int ow = nw / d.sW;
+                if (ow >= d.OW || ow * d.sW != nw) continue;
+                acc = __fmaf_rn(__ldg(gp + ((int64_t)oc * d.OH + oh) * d.OW + ow),
+                                __ldg(kp + kh * d.KW + kw), acc);
+            }
+        }
+    }
+    return acc;
+}
+
+// ------------------------------------------------------------------------------------------------
+// implicit GEMM.  MODE 0: conv2d        C[oc][col] , col = (n, oh, ow), k = (ic, kh, kw)
+//                 MODE 1: grad_input    C[ic][col] , col = (n, h, w),   k = (oc, kh, kw)
+// ------------------------------------------------------------------------------------------------
+constexpr int CG_BK = 16, CG_BN = 128;
+
+// value needs the exact path: non-finite, or non-zero and so small that a product could vanish
+__device__ __forceinline__ bool cg_unsafe(float v)
+{
+    const unsigned ax = __float_as_uint(v) & 0x7FFFFFFFu;
+    return (ax - 1u < 0x1A7FFFFFu) || ax >= 0x7F800000u;  // 0 < |v| < 2^-74, or inf / NaN
+}
+
+template <int BM, int MODE, bool S1>  // S1: stride 1 in both directions (no divisions in the gather)
+__global__ void __launch_bounds__((BM / 8) * (CG_BN / 8))
+conv_gemm_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, float *__restrict__ Out,
+                 ConvDims d)
+{
+    constexpr int NT = (BM / 8) * (CG_BN / 8);
+    constexpr int PA = BM + 4, PB = CG_BN + 4;
+    constexpr int NVA = BM * CG_BK / 4 / NT;     // 4-element groups of A per thread per slab
+    constexpr int NVB = CG_BN * CG_BK / 4 / NT;  // 4-column groups of B per thread per slab
+    __shared__ __align__(16) float As[2][CG_BK][PA];
+    __shared__ __align__(16) float Bs[2][CG_BK][PB];
+
+    const int t = threadIdx.x, lane = t & 31, wid = t >> 5;
+    const int tx = (wid % 2) * 8 + (lane & 7);   // 16 threads along the columns
+    const int ty = (wid / 2) * 4 + (lane >> 3);  // BM / 8 threads along the rows
+    const int g = blockIdx.z;
+    const int KHW = d.KH * d.KW;
+    const int ICg = d.IC / d.groups, OCg = d.OC / d.groups;
+    // GEMM extents and the geometry of the gathered operand
+    const int M = MODE == 0 ? OCg : d.IC;
+    const int K = MODE == 0 ? ICg * KHW : d.OC * KHW;
+    const int outW = MODE == 0 ? d.OW : d.W, outHW = MODE == 0 ? d.OH * d.OW : d.H * d.W;
+    const int srcH = MODE == 0 ? d.H : d.OH, srcW = MODE == 0 ? d.W : d.OW;
+    const int srcPlanes = MODE == 0 ? d.IC : d.OC;
+    const int64_t ncols = (int64_t)d.N * outHW;
+    const int m0 = blockIdx.y * BM;
+    const int64_t col0 = (int64_t)blockIdx.x * CG_BN;
+
+    // ---- B gather: this thread always serves the same 4 columns ----
+    const int bxq = t % (CG_BN / 4), bk0 = t / (CG_BN / 4);  // NT is a multiple of CG_BN / 4
+    int64_t b_base[4];
+    int b_y[4], b_x[4];
+    bool b_ok[4];
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const int64_t col = col0 + bxq * 4 + j;
+        b_ok[j] = col < ncols;
+        const int64_t cc = b_ok[j] ? col : 0;
+        const int n = (int)(cc / outHW), p = (int)(cc % outHW);
+        b_y[j] = p / outW, b_x[j] = p % outW;
+        b_base[j] = ((int64_t)n * srcPlanes + (MODE == 0 ? g * ICg : 0)) * srcH * srcW;
+    }
+    auto gatherB = [&](int k, int j) -> float {
+        if (k >= K || !b_ok[j]) return 0.0f;
+        const int plane = fastdiv(k, d.m40_khw), r = k - plane * KHW;
+        const int kh = fastdiv(r, d.m40_kw), kw = r - kh * d.KW;
+        int sy, sx;
+        if (MODE == 0) {
+            sy = b_y[j] * d.sH - d.pH + kh;
+            sx = b_x[j] * d.sW - d.pW + kw;
+            if (sy < 0 || sy >= srcH || sx < 0 || sx >= srcW) return 0.0f;
+        } else {
+            const int nh = b_y[j] + d.pH - kh, nw = b_x[j] + d.pW - kw;
+            if (nh < 0 || nw < 0) return 0.0f;
+            if (S1) {
+                sy = nh, sx = nw;
+                if (sy >= srcH || sx >= srcW) return 0.0f;
+            } else {
+                sy = nh / d.sH, sx = nw / d.sW;
+                if (sy >= srcH || sx >= srcW || sy * d.sH != nh || sx * d.sW != nw) return 0.0f;
+            }
+        }
+        return __ldg(Src + b_base[j] + ((int64_t)plane * srcH + sy) * srcW + sx);
+    };
+    // ---- A fetch: weights.  MODE 0: row m of [OC][K]; MODE 1: (ic = m, k = (oc, r)) ----
+    auto fetchA = [&](int m, int k) -> float {
+        if (k >= K) return -0.0f;  // K tail: (-0) * (+0) = -0, the identity of the accumulation
+        if (m >= M) return 0.0f;
+        if (MODE == 0) return __ldg(Kw + ((int64_t)(g * OCg + m)) * K + k);
+        const int oc = fastdiv(k, d.m40_khw), r = k - oc * KHW;
+        return __ldg(Kw + ((int64_t)oc * d.IC + m) * KHW + r);
+    };
+
+    float av[NVA][4], bv[NVB][4];
+    bool unsafe = false;
+    auto load_slab = [&](int k0) {
+#pragma unroll
+        for (int i = 0; i < NVA; i++) {
+            const int idx = t + NT * i;
+            const int m = idx / (CG_BK / 4), kq = (idx % (CG_BK / 4)) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                av[i][e] = fetchA(m0 + m, k0 + kq + e);
+                unsafe |= cg_unsafe(av[i][e]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < NVB; i++) {
+            const int k = k0 + bk0 + (NT / (CG_BN / 4)) * i;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                bv[i][j] = gatherB(k, j);
+                unsafe |= cg_unsafe(bv[i][j]);
+            }
+        }
+    };
+    auto store_slab = [&](int buf) {
+#pragma unroll
+        for (int i = 0; i < NVA; i++) {
+            const int idx = t + NT * i;
+            const int m = idx / (CG_BK / 4), kq = (idx % (CG_BK / 4)) * 4;
+#pragma unroll
+            for (int e = 0; e < 4; e++) As[buf][kq + e][m] = av[i][e];
+        }
+#pragma unroll
+        for (int i = 0; i < NVB; i++) {
+            const int kl = bk0 + (NT / (CG_BN / 4)) * i;
+            *reinterpret_cast<float4 *>(&Bs[buf][kl][bxq * 4]) = make_float4(bv[i][0], bv[i][1], bv[i][2], bv[i][3]);
+        }
+    };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+
+    const int nk = (K + CG_BK - 1) / CG_BK;
+    load_slab(0);
+    store_slab(0);
+    __syncthreads();
+    for (int kt = 0; kt < nk; kt++) {
+        const int cur = kt & 1;
+        const bool more = kt + 1 < nk;
+        if (more) load_slab((kt + 1) * CG_BK);
+#pragma unroll
+        for (int k = 0; k < CG_BK; k++) {
+            const float4 a0 = *reinterpret_cast<const float4 *>(&As[cur][k][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4 *>(&As[cur][k][BM / 2 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4 *>(&Bs[cur][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4 *>(&Bs[cur][k][CG_BN / 2 + tx * 4]);
+            const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float b[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+        }
+        if (more) store_slab(cur ^ 1);
+        __syncthreads();
+    }
+    // did any thread of this CTA meet an operand that makes the +0 padding unsafe?
+    const bool redo = __syncthreads_or(unsafe ? 1 : 0) != 0;
+
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : BM / 2 + ty * 4 + i - 4);
+        if (m >= M) continue;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int64_t colq = col0 + (h ? CG_BN / 2 : 0) + tx * 4;
+            if (colq >= ncols) continue;
+            const int n = (int)(colq / outHW), p = (int)(colq % outHW);
+            const int plane = MODE == 0 ? g * OCg + m : m;
+            const int planes = MODE == 0 ? d.OC : d.IC;
+            float c[4] = {acc[i][h * 4 + 0], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]};
+            if (redo) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int64_t col = colq + j;
+                    if (col >= ncols) break;
+                    const int nn = (int)(col / outHW), pp = (int)(col % outHW);
+                    c[j] = MODE == 0 ? conv2d_exact(Src, Kw, d, nn, plane, pp / outW, pp % outW)
+                                     : conv2d_grad_input_exact(Src, Kw, d, nn, plane, pp / outW, pp % outW);
+                }
+            }
+            float *dst = Out + ((int64_t)n * planes + plane) * outHW + p;
+            if (p + 3 < outHW && (outHW & 3) == 0 && (reinterpret_cast<uintptr_t>(Out) & 15u) == 0) {
+                *reinterpret_cast<float4 *>(dst) = make_float4(c[0], c[1], c[2], c[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    const int64_t col = colq + j;
+                    if (col >= ncols) break;
+                    const int nn = (int)(col / outHW), pp = (int)(col % outHW);
+                    Out[((int64_t)nn * planes + plane) * outHW + pp] = c[j];
+                }
+            }
+        }
+    }
+}
+
+template <int MODE>
+int launch_conv_gemm(const float *src, const float *kw, float *out, const ConvDims &d, cudaStream_t st)
+{
+    const int ICg = d.IC / d.groups, OCg = d.OC / d.groups;
+    const int M = MODE == 0 ? OCg : d.IC;
+    const int outHW = MODE == 0 ? d.OH * d.OW : d.H * d.W;
+    const int64_t ncols = (int64_t)d.N * outHW;
+    const int64_t gx = (ncols + CG_BN - 1) / CG_BN;
+    const int groups = MODE == 0 ? d.groups : 1;
+    if (gx > 0x7FFFFFFF || groups > 65535) return REPDL_E_RANGE;
+    (void)ICg;
+    const bool s1 = d.sH == 1 && d.sW == 1;
+    if (M <= 32) {
+        dim3 grid((unsigned)gx, (unsigned)((M + 31) / 32), (unsigned)groups);
+        if (s1)
+            conv_gemm_kernel<32, MODE, true><<<grid, 64, 0, st>>>(src, kw, out, d);
+        else
+            conv_gemm_kernel<32, MODE, false><<<grid, 64, 0, st>>>(src, kw, out, d);
+    } else {
+        dim3 grid((unsigned)gx, (unsigned)((M + 63) / 64), (unsigned)groups);
+        if (grid.y > 65535) return REPDL_E_RANGE;
+        if (s1)
+            conv_gemm_kernel<64, MODE, true><<<grid, 128, 0, st>>>(src, kw, out, d);
+        else
+            conv_gemm_kernel<64, MODE, false><<<grid, 128, 0, st>>>(src, kw, out, d);
+    }
+    return launch_status();
+}
+
+// ------------------------------------------------------------------------------------------------
+// conv2d_grad_kernel: few outputs (OC * IC * KH * KW), each a chain over batch * OH * OW steps that
+// must not be split.  The floor is the latency of the dependent FMA chain (4 cycles per step), so
+// the kernel is built to sit on that floor: a CTA of 4 warps (one per scheduler) owns 8 output
+// channels x 32 weight columns (ic, kh, kw); a thread owns one channel x two adjacent columns, i.e.
+// two independent chains; k = (n, oh, ow) is walked in slabs of 128 through double-buffered shared
+// memory (a slab's 40 loads per thread are all in flight while the previous slab is multiplied,
+// which is what hides the L2 latency with only one warp per scheduler).  Every thread stages four k
+// of the slab for all rows and columns, so (n, oh, ow) is decoded four times per slab and thread;
+// the per-column input offsets are constants of the thread.  Padding
+// taps enter as +0.0 under the same operand watch + exact fallback as the GEMM form above.
+// ------------------------------------------------------------------------------------------------
+__device__ __forceinline__ float conv2d_grad_kernel_exact(const float *__restrict__ GO,
+                                                          const float *__restrict__ I, const ConvDims &d,
+                                                          int oc, int ic, int kh, int kw)
+{
+    float acc = 0.0f;
+    for (int n = 0; n < d.N; n++) {
+        const float *gp = GO + ((int64_t)n * d.OC + oc) * d.OH * d.OW;
+        const float *ip = I + ((int64_t)n * d.IC + ic) * d.H * d.W;
+        for (int oh = 0; oh < d.OH; oh++) {
+            int h = oh * d.sH - d.pH + kh;
+            if (h < 0 || h >= d.H) continue;
+            for (int ow = 0; ow < d.OW; ow++) {
+                int w = ow * d.sW - d.pW + kw;
+                if (w < 0 || w >= d.W) continue;
+                acc = __fmaf_rn(__ldg(gp + oh * d.OW + ow), __ldg(ip + h * d.W + w), acc);
+            }
+        }
+    }
+    return acc;
+}
+
+constexpr int GK_BK = 128, GK_ROWS = 8, GK_THREADS = 128;
+constexpr int GK_KPT = GK_BK / 32;  // k values staged per thread per slab
+
+// COLS = 32: a thread owns two adjacent columns (two chains); COLS = 16: one column, which puts twice
+// as many CTAs on the machine when there are few outputs.
+template <int COLS>
+__global__ void __launch_bounds__(GK_THREADS)
+conv_gk_kernel(const float *__restrict__ GO, const float *__restrict__ I, float *__restrict__ GK,
+               ConvDims d)
+{
+    constexpr int CPT = COLS / 16;      // columns per thread in the compute role
+    constexpr int SCOL = COLS / 4;      // columns staged per thread
+    // row pitches 9 and COLS + 2: the staging stores (one k per thread) spread over the banks, and
+    // the 8-byte fragment loads of Bs stay aligned
+    __shared__ __align__(16) float As[2][GK_BK][GK_ROWS + 1];
+    __shared__ __align__(16) float Bs[2][GK_BK][COLS + 2];
+    const int t = threadIdx.x;
+    const int KHW = d.KH * d.KW, OHW = d.OH * d.OW, HW = d.H * d.W;
+    const int ncols = d.IC * KHW;
+    const int64_t K = (int64_t)d.N * OHW;
+    const int oc0 = blockIdx.y * GK_ROWS, col0 = blockIdx.x * COLS;
+    // compute role: one output channel, CPT adjacent columns
+    const int crow = t / 16, ccol = (t % 16) * CPT;
+    // staging role: k_local = t % 32 + 32 q (q < GK_KPT); rows t/32 + 4 i (i < 2); columns t/32 + 4 i
+    const int sk = t % 32, sq = t / 32;
+    int col_off[SCOL], col_kh[SCOL], col_kw[SCOL];
+    bool col_ok[SCOL];
+#pragma unroll
+    for (int i = 0; i < SCOL; i++) {
+        const int col = col0 + sq + 4 * i;
+        col_ok[i] = col < ncols;
+        const int c = col_ok[i] ? col : 0;
+        const int ic = c / KHW, r = c - ic * KHW;
+        col_kh[i] = r / d.KW, col_kw[i] = r - col_kh[i] * d.KW;
+        col_off[i] = ic * HW + (col_kh[i] - d.pH) * d.W + (col_kw[i] - d.pW);
+    }
+    const bool padded = (d.pH | d.pW) != 0;
+    // (n, p) of this thread's k values, advanced by GK_BK per slab without divisions
+    int kn[GK_KPT], kp[GK_KPT];
+#pragma unroll
+    for (int q = 0; q < GK_KPT; q++) {
+        const int64_t k = sk + 32 * q;
+        kn[q] = (int)(k / OHW);
+        kp[q] = (int)(k - (int64_t)kn[q] * OHW);
+    }
+    float av[GK_KPT][2], bv[GK_KPT][SCOL];
+    bool unsafe = false;
+    auto load_slab = [&]() {  // loads the slab (kn, kp) point at, then advances them by GK_BK
+#pragma unroll
+        for (int q = 0; q < GK_KPT; q++) {
+            const int n = kn[q], p = kp[q];
+            const bool kin = n < d.N;
+            const int oh = fastdiv(p, d.m40_ow), ow = p - oh * d.OW;
+#pragma unroll
+            for (int i = 0; i < 2; i++) {
+                const int oc = oc0 + sq + 4 * i;
+                // K tail: A = -0, B = +0 gives the product -0, the identity of the accumulation
+                av[q][i] = !kin ? -0.0f
+                                : (oc < d.OC ? __ldg(GO + ((int64_t)n * d.OC + oc) * OHW + p) : 0.0f);
+                unsafe |= cg_unsafe(av[q][i]);
+            }
+            const float *ip = I + (int64_t)(kin ? n : 0) * d.IC * HW + (oh * d.sH) * d.W + ow * d.sW;
+#pragma unroll
+            for (int i = 0; i < SCOL; i++) {
+                bool ok = kin && col_ok[i];
+                if (padded) {
+                    const int h = oh * d.sH - d.pH + col_kh[i], w = ow * d.sW - d.pW + col_kw[i];
+                    ok = ok && h >= 0 && h < d.H && w >= 0 && w < d.W;
+                }
+                bv[q][i] = ok ? __ldg(ip + col_off[i]) : 0.0f;
+                unsafe |= cg_unsafe(bv[q][i]);
+            }
+            kp[q] += GK_BK;
+            while (kp[q] >= OHW) kp[q] -= OHW, kn[q]++;
+        }
+    };
+    auto store_slab = [&](int buf) {
+#pragma unroll
+        for (int q = 0; q < GK_KPT; q++) {
+#pragma unroll
+            for (int i = 0; i < 2; i++) As[buf][sk + 32 * q][sq + 4 * i] = av[q][i];
+#pragma unroll
+            for (int i = 0; i < SCOL; i++) Bs[buf][sk + 32 * q][sq + 4 * i] = bv[q][i];
+        }
+    };
+    float acc[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; j++) acc[j] = 0.0f;
+    const int64_t nslab = (K + GK_BK - 1) / GK_BK;
+    load_slab();
+    store_slab(0);
+    __syncthreads();
+    for (int64_t kt = 0; kt < nslab; kt++) {
+        const int cur = (int)(kt & 1);
+        const bool more = kt + 1 < nslab;
+        if (more) load_slab();
+#pragma unroll
+        for (int k = 0; k < GK_BK; k++) {
+            const float a = As[cur][k][crow];
+            if (CPT == 2) {
+                const float2 b = *reinterpret_cast<const float2 *>(&Bs[cur][k][ccol]);
+                acc[0] = __fmaf_rn(a, b.x, acc[0]);
+                acc[CPT - 1] = __fmaf_rn(a, b.y, acc[CPT - 1]);
+            } else {
+                acc[0] = __fmaf_rn(a, Bs[cur][k][ccol], acc[0]);
+            }
+        }
+        if (more) store_slab(cur ^ 1);
+        __syncthreads();
+    }
+    const bool redo = __syncthreads_or(unsafe ? 1 : 0) != 0;
+    const int oc = oc0 + crow;
+    if (oc < d.OC) {
+#pragma unroll
+        for (int j = 0; j < CPT; j++) {
+            const int col = col0 + ccol + j;
+            if (col >= ncols) continue;
+            float v = acc[j];
+            if (redo) {
+                const int ic = col / KHW, r = col - ic * KHW;
+                v = conv2d_grad_kernel_exact(GO, I, d, oc, ic, r / d.KW, r % d.KW);
+            }
+            GK[(int64_t)oc * ncols + col] = v;
+        }
+    }
+}
+
 int fill_dims(ConvDims &d, int64_t N, int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH,
               int64_t KW, int64_t sH, int64_t sW, int64_t pH, int64_t pW, int64_t groups)
 {
@@ -140,6 +594,10 @@ int fill_dims(ConvDims &d, int64_t N, int64_t IC, int64_t H, int64_t W, int64_t 
     d.groups = (int)groups;
     d.OH = (int)((H + 2 * pH - KH) / sH + 1);
     d.OW = (int)((W + 2 * pW - KW) / sW + 1);
+    const unsigned long long khw = (unsigned long long)(KH * KW), kwv = (unsigned long long)KW;
+    d.m40_khw = ((1ull << 40) + khw - 1) / khw;
+    d.m40_kw = ((1ull << 40) + kwv - 1) / kwv;
+    d.m40_ow = ((1ull << 40) + (unsigned long long)d.OW - 1) / (unsigned long long)d.OW;
     return REPDL_OK;
 }
 
@@ -168,6 +626,9 @@ extern "C" int repdl_b200_conv2d(const float *input, const float *kernel, float 
     int64_t total = (int64_t)d.N * d.OC * d.OH * d.OW;
     if (total == 0) return REPDL_OK;
     if (!input || !kernel || !output) return REPDL_E_NULL;
+    if ((int64_t)d.KH * d.KW <= 64 && (int64_t)d.IC * d.KH * d.KW < (1 << 24) &&
+        (int64_t)d.N * d.OH * d.OW >= 64)
+        return launch_conv_gemm<0>(input, kernel, output, d, (cudaStream_t)stream);
     unsigned blocks;
     if ((e = blocks_for(total, blocks))) return e;
     conv2d_direct_kernel<<<blocks, CONV_THREADS, 0, (cudaStream_t)stream>>>(input, kernel, output,
@@ -188,6 +649,9 @@ extern "C" int repdl_b200_conv2d_grad_input(const float *grad_output, const floa
     int64_t total = (int64_t)d.N * d.IC * d.H * d.W;
     if (total == 0) return REPDL_OK;
     if (!grad_output || !kernel || !grad_input) return REPDL_E_NULL;
+    if ((int64_t)d.KH * d.KW <= 64 && (int64_t)d.OC * d.KH * d.KW < (1 << 24) &&
+        (int64_t)d.N * d.H * d.W >= 64)
+        return launch_conv_gemm<1>(grad_output, kernel, grad_input, d, (cudaStream_t)stream);
     unsigned blocks;
     if ((e = blocks_for(total, blocks))) return e;
     conv2d_grad_input_direct_kernel<<<blocks, CONV_THREADS, 0, (cudaStream_t)stream>>>(
@@ -207,6 +671,22 @@ extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const flo
     if (e) return e;
     int64_t total = (int64_t)d.OC * d.IC * d.KH * d.KW;
     if (!grad_output || !input || !grad_kernel) return REPDL_E_NULL;
+    if ((int64_t)d.N * d.OH * d.OW >= 256 && (int64_t)d.IC * d.KH * d.KW < 0x7FFFFFFF &&
+        (int64_t)d.IC * d.H * d.W < 0x7FFFFFFF) {
+        const int ncols = d.IC * d.KH * d.KW;
+        const unsigned gy = (unsigned)((d.OC + GK_ROWS - 1) / GK_ROWS);
+        // few outputs: one chain per thread spreads them over twice as many SMs
+        const bool narrow = (int64_t)((ncols + 31) / 32) * gy < 2 * (int64_t)sm_count();
+        if (gy <= 65535 && d.OW < 65536 && (int64_t)d.OH * d.OW < (1 << 24)) {
+            if (narrow)
+                conv_gk_kernel<16><<<dim3((unsigned)((ncols + 15) / 16), gy), GK_THREADS, 0,
+                                     (cudaStream_t)stream>>>(grad_output, input, grad_kernel, d);
+            else
+                conv_gk_kernel<32><<<dim3((unsigned)((ncols + 31) / 32), gy), GK_THREADS, 0,
+                                     (cudaStream_t)stream>>>(grad_output, input, grad_kernel, d);
+            return launch_status();
+        }
+    }
     unsigned blocks;
     if ((e = blocks_for(total, blocks))) return e;
     conv2d_grad_kernel_direct_kernel<<<blocks, CONV_THREADS, 0, (cudaStream_t)stream>>>(

@@ -202,6 +202,19 @@ chain_sum_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t n
             int cnt = left < CHAIN_TILE ? (int)left : CHAIN_TILE;
             const float4 *b4 = reinterpret_cast<const float4 *>(buf[cur]);
             int i = 0;
+            // 8 loads ahead of the adds: the walk then runs at the latency of the FADD chain
+            for (; i + 32 <= cnt; i += 32) {
+                float4 v[8];
+#pragma unroll
+                for (int u = 0; u < 8; u++) v[u] = b4[(i >> 2) + u];
+#pragma unroll
+                for (int u = 0; u < 8; u++) {
+                    s = __fadd_rn(s, v[u].x);
+                    s = __fadd_rn(s, v[u].y);
+                    s = __fadd_rn(s, v[u].z);
+                    s = __fadd_rn(s, v[u].w);
+                }
+            }
             for (; i + 4 <= cnt; i += 4) {
                 float4 v = b4[i >> 2];
                 s = __fadd_rn(s, v.x);
