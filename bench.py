@@ -240,6 +240,22 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
             want = gold["c3_sum1d_2p30"]["state_after_chunk_hex"][flat.numel() // (1 << 24) - 1]
             rec["bits_equal_reference_cpu"] = (
                 "%08x" % (y.cpu().view(torch.int32).item() & 0xFFFFFFFF)) == want
+        # how the walk went: opened nodes / tiles / leaves and the walker's cycle counters, which the
+        # kernel leaves in the first bytes of its scratch buffer
+        from repdl_b200._cabi import check, lib
+        nb = lib.repdl_b200_sum1d_scratch_bytes(flat.numel())
+        if nb >= 80:
+            sc = torch.zeros(nb, dtype=torch.uint8, device=flat.device)
+            o = torch.zeros((), device=flat.device)
+            check(lib.repdl_b200_sum1d(flat.data_ptr(), o.data_ptr(), flat.numel(), 1.0, sc.data_ptr(), nb, None),
+                  "sum1d")
+            torch.cuda.synchronize()
+            opens = sc[:16].view(torch.int32).tolist()
+            cyc = sc[16:64].view(torch.int64).tolist()
+            rec["walk"] = {"nodes": opens[3], "opened_nodes": opens[0], "opened_tiles": opens[1],
+                           "opened_leaves": opens[2], "cycles_total": cyc[0], "cycles_prepare_nodes": cyc[1],
+                           "cycles_leaf_level": cyc[2], "cycles_leaf_adds": cyc[3],
+                           "cycles_leaf_rebuild": cyc[4]}
         out["sum1d chain [%d]" % flat.numel()] = rec
     return out
 
@@ -385,7 +401,13 @@ def main():
                        "parallelism": "rows/%d" % world, "collective": sh.mode,
                        "l2": "operands (3 GiB) exceed the 126 MB L2"},
             "roofline": {"bound": "fp32_ffma", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
-                         "frac": achieved / peak, "traffic": None,
+                         "frac": achieved / peak,
+                         # DRAM bytes of one rank's launch: the ncu capture of the 16384^3 launch
+                         # (profiles/sgemm_mm16384_launch_list_and_dram.md: 35.58 GB), scaled by the
+                         # rows a rank computes (B is streamed once per group of 8 tile rows, so the
+                         # traffic is proportional to the rows); null for other sizes
+                         "traffic": (35.58e9 / world if n == 16384 else None),
+                         "algorithmic_bytes": 4.0 * (n * n / world + n * n + n * n / world),
                          "peak_source": "FFMA-only probe kernel timed in this run",
                          "peak_nominal": 148 * 128 * 2 * 1.965e9 / 1e12,
                          "kernel_ms": kernel_ms},

@@ -9,23 +9,31 @@
 namespace repdl_b200 {
 namespace {
 
-// exp/log read one table entry per element at a data-dependent index; the tables (256 B and
-// 1.5 KB) are staged in shared memory once per CTA so that those reads never leave the SM.
+// exp/log read one table entry per element at a data-dependent index; the tables (1 KB and
+// 2 KB) are staged in shared memory once per CTA so that those reads never leave the SM.
+// (Replicating every entry once per lane to make the lookups bank-conflict-free was tried and is
+// slower: 32-48 KB per CTA costs more occupancy than the conflicts cost bandwidth.)
 struct SmemTables {
-    const double *p;  // [0,32) 2^(j/32); [32,96) c_i; [96,160) -log c_i hi; [160,224) lo
+    const double *p;  // [0, N_exp) 2^(j/N); then N_log pairs (c_i, -log c_i), 16-byte aligned
     __device__ __forceinline__ double exp_t(int j) const { return p[j]; }
-    __device__ __forceinline__ double log_c(int i) const { return p[32 + i]; }
-    __device__ __forceinline__ double log_t_hi(int i) const { return p[96 + i]; }
-    __device__ __forceinline__ double log_t_lo(int i) const { return p[160 + i]; }
+    __device__ __forceinline__ void log_ct(int i, double &c, double &t_hi) const
+    {
+        const double2 v = *reinterpret_cast<const double2 *>(p + CRM_EXP_N + 2 * i);
+        c = v.x, t_hi = v.y;
+    }
 };
-constexpr int TABLE_DOUBLES = 224;
+constexpr int TABLE_DOUBLES = CRM_EXP_N + 2 * CRM_LOG_N;
 
 __device__ __forceinline__ void stage_tables(double *sm)
 {
     for (int i = threadIdx.x; i < TABLE_DOUBLES; i += blockDim.x) {
-        unsigned long long b = i < 32 ? CRM_EXP_T_HI[i]
-                             : i < 96 ? CRM_LOG_C[i - 32]
-                             : i < 160 ? CRM_LOG_T_HI[i - 96] : CRM_LOG_T_LO[i - 160];
+        unsigned long long b;
+        if (i < CRM_EXP_N) {
+            b = CRM_EXP_T_HI[i];
+        } else {
+            const int e = i - CRM_EXP_N;
+            b = (e & 1) ? CRM_LOG_T_HI[e >> 1] : CRM_LOG_C[e >> 1];
+        }
         sm[i] = __longlong_as_double((long long)b);
     }
     __syncthreads();
@@ -58,13 +66,21 @@ struct OpLog {
     }
     __device__ __forceinline__ float slow(float x) const { return crm_log_slow(x); }
 };
+// x / d for one divisor d: (float)((double)x * rd) with rd = 1.0 / (double)d.  The product is within
+// 2^-52 (relative) of the exact quotient, and the quotient of two fp32 values stays at least 2^-49
+// (relative) away from every fp32 rounding midpoint (|a/b - c/2^j| >= 1/(b 2^j) for 24-bit a, b and
+// odd c), so the double rounding cannot change the result: this IS the IEEE fp32 quotient, with no
+// slow path for extreme exponents.  (Checked against x / d for all 2^32 x and a dozen divisors on
+// the CPU.)  Only NaN results take the branch, for the x86 payload rules of cr_div.
 struct OpDivScalar {
     static constexpr bool kTables = false;
     float d;
+    double rd;
     __device__ __forceinline__ float fast(float x, SmemTables, bool &slow) const
     {
-        slow = false;
-        return cr_div(x, d);
+        const float q = __double2float_rn(__dmul_rn((double)x, rd));
+        slow = q != q;
+        return q;
     }
     __device__ __forceinline__ float slow(float x) const { return cr_div(x, d); }
 };
@@ -95,7 +111,7 @@ __global__ void __launch_bounds__(EW_THREADS)
 unary_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t nvec, Op op)
 {
     // nvec = number of float4 groups; x and y are 16-byte aligned
-    __shared__ double tables[Op::kTables ? TABLE_DOUBLES : 1];
+    __shared__ __align__(16) double tables[Op::kTables ? TABLE_DOUBLES : 2];
     if (Op::kTables) stage_tables(tables);
     const SmemTables tab{tables};
     const int64_t stride = (int64_t)gridDim.x * EW_THREADS * EW_VEC_PER_THREAD;
@@ -121,7 +137,7 @@ template <class Op>
 __global__ void __launch_bounds__(EW_THREADS)
 unary_scalar_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t n, Op op)
 {
-    __shared__ double tables[Op::kTables ? TABLE_DOUBLES : 1];
+    __shared__ __align__(16) double tables[Op::kTables ? TABLE_DOUBLES : 2];
     if (Op::kTables) stage_tables(tables);
     const SmemTables tab{tables};
     const int64_t stride = (int64_t)gridDim.x * EW_THREADS;
@@ -144,10 +160,10 @@ div_tensor_kernel(const float *__restrict__ x, const float *__restrict__ d, floa
         y[i] = cr_div(__ldg(x + i), __ldg(d + i));
 }
 
-static unsigned grid_for(int64_t work_items, int per_block)
+static unsigned grid_for(int64_t work_items, int per_block, int per_sm = 8)
 {
     int64_t blocks = (work_items + per_block - 1) / per_block;
-    int64_t cap = (int64_t)sm_count() * 8;
+    int64_t cap = (int64_t)sm_count() * per_sm;
     if (blocks > cap) blocks = cap;
     if (blocks < 1) blocks = 1;
     return (unsigned)blocks;
@@ -206,7 +222,7 @@ extern "C" int repdl_b200_div_scalar(const float *x, float divisor, float *y, in
                                      void *stream)
 {
     clear_stale_error();
-    return launch_unary(x, y, n, OpDivScalar{divisor}, stream);
+    return launch_unary(x, y, n, OpDivScalar{divisor, 1.0 / (double)divisor}, stream);
 }
 
 extern "C" int repdl_b200_div(const float *x, const float *divisor, float *y, int64_t n,

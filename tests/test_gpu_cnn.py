@@ -92,7 +92,18 @@ for step in range(3):
 # the reference's Adam on top of these kernels runs too (repdl/optim.py)
 opt = repdl.optim.Adam(model.parameters(), lr=0.01)
 loss = loss_fn(model(x), y); opt.zero_grad(); loss.backward(); opt.step()
-print(json.dumps(out))
+# batch norm (repdl/nn/batchnorm.py, repdl/func.py) is built from the same operators: the reference's
+# own CPU backend and this package's CUDA backend must agree bit for bit, forward and backward
+def bn_run(dev):
+    torch.manual_seed(5)
+    net = repdl.from_torch_module(torch.nn.Sequential(
+        torch.nn.Conv2d(3, 8, 3, padding=1), torch.nn.BatchNorm2d(8), torch.nn.ReLU(), torch.nn.Flatten(),
+        torch.nn.Linear(8 * 6 * 6, 4))).to(dev)  # (the reference's BatchNorm1d backward raises on its own CPU backend)
+    xi = torch.rand(10, 3, 6, 6).to(dev); yi = torch.randint(0, 4, (10,)).to(dev)
+    l = repdl.nn.CrossEntropyLoss()(net(xi), yi); l.backward()
+    return [sha(l)] + [sha(p.grad) for p in net.parameters()]
+bn_cpu, bn_gpu = bn_run("cpu"), bn_run("cuda")
+print(json.dumps(dict(steps=out, bn_equal=bn_cpu == bn_gpu, bn_n=len(bn_cpu))))
 """
 
 
@@ -108,6 +119,8 @@ def test_reference_python_layers_run_unchanged_on_the_dropin():
     res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
     assert res.returncode == 0, res.stderr[-2000:]
     got = json.loads(res.stdout.strip().splitlines()[-1])
+    assert got["bn_equal"] and got["bn_n"] == 7, got
+    got = got["steps"]
     want = {s["step"]: s for s in json.load(open(GOLD))["steps"]}
     for rec in got:
         assert rec["logits"] == want[rec["step"]]["logits"], rec["step"]
