@@ -260,6 +260,56 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
     return out
 
 
+def cnn_step_bench(steps, warmup):
+    """Config 4: conv-relu-conv-relu-maxpool-flatten-linear-relu-linear-cross-entropy, batch 256, SGD
+    lr 0.01, same batch every step.  Reports ms per training step and checks the parameter hashes
+    of the first steps against the reference's CPU run."""
+    from repdl_b200 import nn as rnn
+    from repdl_b200 import workloads
+    torch.manual_seed(3)
+    model = rnn.from_torch_module(workloads.cnn_torch_model())
+    x, y = workloads.cnn_batch(256)
+    model, x, y = model.cuda(), x.cuda(), y.cuda()
+    loss_fn = rnn.CrossEntropyLoss()
+
+    def phash():
+        h = hashlib.sha256()
+        for p in model.parameters():
+            h.update(p.data.cpu().numpy().tobytes())
+        return h.hexdigest()
+
+    def step():
+        for p in model.parameters():
+            p.grad = None
+        loss = loss_fn(model(x), y)
+        loss.backward()
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(p.grad.mul(-0.01))
+
+    gpath = os.path.join(ROOT, "tests", "golden", "cnn_steps.json")
+    parity = None
+    if os.path.exists(gpath):
+        want = {s["step"]: s["params"] for s in json.load(open(gpath))["steps"]}
+        ok = True
+        for i in range(3):
+            step()
+            ok = ok and phash() == want[i]
+        parity = "parameter sha256 of steps 0-2 equal to reference CPU run" if ok else "MISMATCH"
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    e1.synchronize()
+    ms = e0.elapsed_time(e1) / steps
+    return {"workload": "cnn training step (config 4), batch 256", "ms_per_step": ms,
+            "GFLOP/s": 18.3 / ms * 1e3, "steps": steps, "parity": parity}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -270,9 +320,10 @@ def main():
     ap.add_argument("--mode", default="auto", choices=["auto", "nccl", "p2p"])
     ap.add_argument("--ref-rows", type=int, default=16)
     ap.add_argument("--cpu-budget", type=float, default=15.0)
-    ap.add_argument("--workload", default="mm", choices=["mm", "crmath", "sums"],
+    ap.add_argument("--workload", default="mm", choices=["mm", "crmath", "sums", "cnn"],
                     help="mm: the headline product; crmath / sums: only the HBM-bound kernels of "
-                         "configs 2 / 3 at --elements (used for profiling captures)")
+                         "configs 2 / 3 at --elements; cnn: the config-4 training step "
+                         "(these three are used for profiling captures)")
     ap.add_argument("--elements", type=int, default=1 << 28)
     ap.add_argument("--no-extra", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -290,6 +341,11 @@ def main():
     from repdl_b200 import workloads
     from repdl_b200.dist import ShardedMM, mm_from_host
 
+    if args.workload == "cnn":
+        if rank == 0:
+            torch.cuda.set_device(local_rank)
+            print(json.dumps(cnn_step_bench(args.steps, args.warmup)), flush=True)
+        return
     if args.workload != "mm":
         if rank == 0:
             torch.cuda.set_device(local_rank)

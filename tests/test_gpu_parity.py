@@ -69,6 +69,9 @@ def test_unaligned_pointers(ops):
     assert bits_equal(ops.mm(amd, bmd), oracle.mm(am.contiguous(), bm.contiguous()))
     r = torch.randn(33 * 64 + 1, generator=g)
     assert bits_equal(ops.sum2d_dim1(r.cuda()[1:].view(33, 64)), oracle.sum2d_dim1(r[1:].view(33, 64)))
+    # a long chain (summarised path) that starts 4 bytes past a 16-byte boundary and ends mid-node
+    c = torch.randn(250001, generator=g) * 300.0
+    assert bits_equal(ops.sum1d(c.cuda()[1:]), oracle.sum1d(c[1:].contiguous()))
 
 
 def test_results_do_not_depend_on_run(ops):
