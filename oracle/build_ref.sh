@@ -4,9 +4,9 @@
 # Builds the UNMODIFIED microsoft/RepDL reference into oracle/_ref/ so that the
 # C restatement in this folder (and the CUDA kernels) can be checked against the
 # reference's own CPU backend.  Nothing is copied into the repository: the
-# sources are compiled from where they lie ($REPDL_REFERENCE, default
-# /root/reference) through a scratch copy under /tmp, because the reference's
-# setup.py writes build/ next to itself and the mount is read-only.
+# sources are compiled from where they lie (the directory named by
+# $REPDL_REFERENCE) through a scratch copy in the temp directory, because the
+# reference's setup.py writes build/ next to itself and the tree may be read-only.
 #
 # Outputs (all git-ignored, all under oracle/_ref/):
 #   site/repdl/...                    the reference Python package
