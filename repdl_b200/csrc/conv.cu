@@ -419,9 +419,11 @@ int launch_conv_gemm(const float *src, const float *kw, float *out, const ConvDi
 // ------------------------------------------------------------------------------------------------
 // conv2d_grad_kernel: few outputs (OC * IC * KH * KW), each a chain over batch * OH * OW steps that
 // must not be split.  The floor is the latency of the dependent FMA chain (4 cycles per step), so
-// the kernel is built to sit on that floor: a CTA of 4 warps (one per scheduler) owns 8 output
-// channels x 32 weight columns (ic, kh, kw); a thread owns one channel x two adjacent columns, i.e.
-// two independent chains; k = (n, oh, ow) is walked in slabs of 128 through double-buffered shared
+// the kernel is built to sit near that floor: a CTA owns 8 output channels x 32 (or 16) weight
+// columns (ic, kh, kw); its first 4 warps (one per scheduler) only multiply -- a thread owns one
+// channel x two (one) adjacent columns and issues two shared-memory loads and two (one) FMAs per
+// step -- while 4 more warps do nothing but stage the next slab, so the chains never wait for address
+// arithmetic or global loads.  k = (n, oh, ow) is walked in slabs of 128 through double-buffered shared
 // memory (a slab's 40 loads per thread are all in flight while the previous slab is multiplied,
 // which is what hides the L2 latency with only one warp per scheduler).  Every thread stages four k
 // of the slab for all rows and columns, so (n, oh, ow) is decoded four times per slab and thread;
@@ -449,7 +451,7 @@ __device__ __forceinline__ float conv2d_grad_kernel_exact(const float *__restric
     return acc;
 }
 
-constexpr int GK_BK = 128, GK_ROWS = 8, GK_THREADS = 128;
+constexpr int GK_BK = 128, GK_ROWS = 8, GK_THREADS = 256;  // 4 compute warps + 4 staging warps
 constexpr int GK_KPT = GK_BK / 32;  // k values staged per thread per slab
 
 // COLS = 32: a thread owns two adjacent columns (two chains); COLS = 16: one column, which puts twice
@@ -461,11 +463,15 @@ conv_gk_kernel(const float *__restrict__ GO, const float *__restrict__ I, float 
 {
     constexpr int CPT = COLS / 16;      // columns per thread in the compute role
     constexpr int SCOL = COLS / 4;      // columns staged per thread
-    // row pitches 9 and COLS + 2: the staging stores (one k per thread) spread over the banks, and
-    // the 8-byte fragment loads of Bs stay aligned
-    __shared__ __align__(16) float As[2][GK_BK][GK_ROWS + 1];
-    __shared__ __align__(16) float Bs[2][GK_BK][COLS + 2];
-    const int t = threadIdx.x;
+    // k is the contiguous index of both slabs (pitch GK_BK + 4 floats), so a multiplying thread
+    // fetches four consecutive k of its row / column with one LDS.128 -- a quarter of the loads, and
+    // each load is four steps ahead of its last use; the staging threads (one k each) store to
+    // consecutive addresses
+    constexpr int PK = GK_BK + 4;
+    __shared__ __align__(16) float As[2][GK_ROWS][PK];
+    __shared__ __align__(16) float Bs[2][COLS][PK];
+    const bool producer = threadIdx.x >= 128;
+    const int t = threadIdx.x & 127;  // index within the role
     const int KHW = d.KH * d.KW, OHW = d.OH * d.OW, HW = d.H * d.W;
     const int ncols = d.IC * KHW;
     const int64_t K = (int64_t)d.N * OHW;
@@ -494,9 +500,12 @@ conv_gk_kernel(const float *__restrict__ GO, const float *__restrict__ I, float 
         kn[q] = (int)(k / OHW);
         kp[q] = (int)(k - (int64_t)kn[q] * OHW);
     }
-    float av[GK_KPT][2], bv[GK_KPT][SCOL];
+    // two register sets: while one slab is being written to shared memory the loads of the next
+    // one are already in flight (the producers run two slabs ahead of the multiplying warps)
+    float avA[GK_KPT][2], bvA[GK_KPT][SCOL], avB[GK_KPT][2], bvB[GK_KPT][SCOL];
     bool unsafe = false;
-    auto load_slab = [&]() {  // loads the slab (kn, kp) point at, then advances them by GK_BK
+    auto load_slab = [&](float (&av)[GK_KPT][2], float (&bv)[GK_KPT][SCOL]) {
+        // loads the slab (kn, kp) point at, then advances them by GK_BK
 #pragma unroll
         for (int q = 0; q < GK_KPT; q++) {
             const int n = kn[q], p = kp[q];
@@ -525,43 +534,61 @@ conv_gk_kernel(const float *__restrict__ GO, const float *__restrict__ I, float 
             while (kp[q] >= OHW) kp[q] -= OHW, kn[q]++;
         }
     };
-    auto store_slab = [&](int buf) {
+    auto store_slab = [&](int buf, const float (&av)[GK_KPT][2], const float (&bv)[GK_KPT][SCOL]) {
 #pragma unroll
         for (int q = 0; q < GK_KPT; q++) {
 #pragma unroll
-            for (int i = 0; i < 2; i++) As[buf][sk + 32 * q][sq + 4 * i] = av[q][i];
+            for (int i = 0; i < 2; i++) As[buf][sq + 4 * i][sk + 32 * q] = av[q][i];
 #pragma unroll
-            for (int i = 0; i < SCOL; i++) Bs[buf][sk + 32 * q][sq + 4 * i] = bv[q][i];
+            for (int i = 0; i < SCOL; i++) Bs[buf][sq + 4 * i][sk + 32 * q] = bv[q][i];
+        }
+    };
+    auto multiply_slab = [&](int cur, float (&acc)[CPT]) {
+#pragma unroll
+        for (int k = 0; k < GK_BK; k += 4) {
+            const float4 a = *reinterpret_cast<const float4 *>(&As[cur][crow][k]);
+#pragma unroll
+            for (int j = 0; j < CPT; j++) {
+                const float4 b = *reinterpret_cast<const float4 *>(&Bs[cur][ccol + j][k]);
+                acc[j] = __fmaf_rn(a.x, b.x, acc[j]);
+                acc[j] = __fmaf_rn(a.y, b.y, acc[j]);
+                acc[j] = __fmaf_rn(a.z, b.z, acc[j]);
+                acc[j] = __fmaf_rn(a.w, b.w, acc[j]);
+            }
         }
     };
     float acc[CPT];
 #pragma unroll
     for (int j = 0; j < CPT; j++) acc[j] = 0.0f;
     const int64_t nslab = (K + GK_BK - 1) / GK_BK;
-    load_slab();
-    store_slab(0);
+    if (producer) {
+        load_slab(avA, bvA);            // slab 0
+        store_slab(0, avA, bvA);
+        if (nslab > 1) load_slab(avA, bvA);  // slab 1 stays in flight in set A
+    }
     __syncthreads();
-    for (int64_t kt = 0; kt < nslab; kt++) {
-        const int cur = (int)(kt & 1);
-        const bool more = kt + 1 < nslab;
-        if (more) load_slab();
-#pragma unroll
-        for (int k = 0; k < GK_BK; k++) {
-            const float a = As[cur][k][crow];
-            if (CPT == 2) {
-                const float2 b = *reinterpret_cast<const float2 *>(&Bs[cur][k][ccol]);
-                acc[0] = __fmaf_rn(a, b.x, acc[0]);
-                acc[CPT - 1] = __fmaf_rn(a, b.y, acc[CPT - 1]);
-            } else {
-                acc[0] = __fmaf_rn(a, Bs[cur][k][ccol], acc[0]);
-            }
+    // iterations come in pairs so that the register sets have fixed names: entering an even
+    // iteration kt, slab kt + 1 is in set A; entering an odd one it is in set B
+    for (int64_t kt = 0; kt < nslab; kt += 2) {
+        if (producer) {
+            if (kt + 2 < nslab) load_slab(avB, bvB);
+            if (kt + 1 < nslab) store_slab(1, avA, bvA);
+        } else {
+            multiply_slab(0, acc);
         }
-        if (more) store_slab(cur ^ 1);
+        __syncthreads();
+        if (kt + 1 >= nslab) break;
+        if (producer) {
+            if (kt + 3 < nslab) load_slab(avA, bvA);
+            if (kt + 2 < nslab) store_slab(0, avB, bvB);
+        } else {
+            multiply_slab(1, acc);
+        }
         __syncthreads();
     }
     const bool redo = __syncthreads_or(unsafe ? 1 : 0) != 0;
     const int oc = oc0 + crow;
-    if (oc < d.OC) {
+    if (!producer && oc < d.OC) {
 #pragma unroll
         for (int j = 0; j < CPT; j++) {
             const int col = col0 + ccol + j;
@@ -575,6 +602,292 @@ conv_gk_kernel(const float *__restrict__ GO, const float *__restrict__ I, float 
         }
     }
 }
+
+// ------------------------------------------------------------------------------------------------
+// conv2d_grad_kernel, row-chunk form (the one used whenever an image's output rows give chunks of a
+// useful length).  Same split of roles as above -- 4 warps that only multiply, one chain per thread
+// and column, and 4 warps that only stage -- but the staging warps never touch a value: k is walked
+// image by image in chunks of R whole output rows (or of <= 256 columns of one row when rows are
+// longer than that), every operand element goes global -> shared with one 4-byte cp.async (16-byte
+// for grad_output when its rows allow it), three chunks are in flight, and the (row, column) decoding
+// of a thread's elements is the same for every chunk, so it is done once.  What is left per element
+// is an integer add, the address and the copy.  Padding taps and the ragged ends are zero-filled by
+// the copy itself (src-size 0), so only a padded convolution needs the operand watch: there the
+// staging threads read back what they copied when it has landed, and the CTA falls back to the exact
+// loop for its outputs if a non-finite or vanishing value was seen.
+// ------------------------------------------------------------------------------------------------
+constexpr int GKR_KMAX = 256, GKR_PITCH = GKR_KMAX + 4, GKR_STAGES = 3;
+
+__device__ __forceinline__ void cp_async_4z(float *smem_dst, const float *gmem_src, bool ok)
+{
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = ok ? 4 : 0;  // 0: nothing is read, the word is zero-filled
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes)
+                 : "memory");
+}
+__device__ __forceinline__ void cp_async_16z(float *smem_dst, const float *gmem_src, bool ok)
+{
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    const int bytes = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes)
+                 : "memory");
+}
+
+// position of a chunk: image n, first output row oh0, first output column ow0
+struct GkChunk {
+    int n, oh0, ow0;
+};
+
+template <int COLS, bool PADDED>
+__global__ void __launch_bounds__(GK_THREADS)
+conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, float *__restrict__ GK,
+                    ConvDims d, int segW, int R, int a16, long long nchunks)
+{
+    extern __shared__ __align__(16) float gkr_smem[];
+    constexpr int STAGE = (GK_ROWS + COLS) * GKR_PITCH;
+    constexpr int CPT = COLS / 16;
+    const bool producer = threadIdx.x >= 128;
+    const int t = threadIdx.x & 127;
+    const int KHW = d.KH * d.KW, OHW = d.OH * d.OW, HW = d.H * d.W;
+    const int ncols = d.IC * KHW;
+    const int oc0 = blockIdx.y * GK_ROWS, col0 = blockIdx.x * COLS;
+
+    auto chunk_len = [&](const GkChunk &c) {
+        const int rows = min(R, d.OH - c.oh0);
+        return segW == d.OW ? rows * d.OW : min(segW, d.OW - c.ow0);
+    };
+    auto advance = [&](GkChunk &c) {
+        c.ow0 += segW;
+        if (c.ow0 >= d.OW) {
+            c.ow0 = 0;
+            c.oh0 += R;
+            if (c.oh0 >= d.OH) c.oh0 = 0, c.n++;
+        }
+    };
+
+    // staging role: this thread's elements of a chunk are k_local = t and t + 128 of every row and column
+    int boff[2], hb[2], wb[2];
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int kl = t + 128 * j;
+        const int r = kl / segW, c = kl - r * segW;
+        boff[j] = r * d.sH * d.W + c * d.sW;
+        hb[j] = r * d.sH - d.pH;
+        wb[j] = c * d.sW - d.pW;
+    }
+    int col_off[COLS], col_hw[COLS];
+#pragma unroll
+    for (int c = 0; c < COLS; c++) {
+        const int col = min(col0 + c, ncols - 1);
+        const int ic = col / KHW, r = col - ic * KHW;
+        const int kh = r / d.KW, kw = r - kh * d.KW;
+        col_off[c] = ic * HW + (kh - d.pH) * d.W + (kw - d.pW);
+        col_hw[c] = (kh << 16) | kw;
+    }
+    const int nvalid_cols = ncols - col0;
+    bool unsafe = false;
+
+    auto issue = [&](int stage, const GkChunk &c) {
+        float *As = gkr_smem + stage * STAGE, *Bs = As + GK_ROWS * GKR_PITCH;
+        const int len = chunk_len(c);
+        const float *ga = GO + ((int64_t)c.n * d.OC + oc0) * OHW + c.oh0 * d.OW + c.ow0;
+        if (a16) {
+            const int row = t / 16, l = t % 16;
+            const bool ok = oc0 + row < d.OC;
+            const float *src = ok ? ga + (int64_t)row * OHW : GO;
+#pragma unroll
+            for (int m = 0; m < GKR_KMAX / 64; m++) {
+                const int q = 4 * (l + 16 * m);
+                if (q < len) cp_async_16z(&As[row * GKR_PITCH + q], ok ? src + q : GO, ok);
+            }
+        } else {
+#pragma unroll
+            for (int j = 0; j < 2; j++) {
+                const int kl = t + 128 * j;
+                if (kl >= len) continue;
+#pragma unroll
+                for (int row = 0; row < GK_ROWS; row++) {
+                    const bool ok = oc0 + row < d.OC;
+                    cp_async_4z(&As[row * GKR_PITCH + kl], ok ? ga + (int64_t)row * OHW + kl : GO, ok);
+                }
+            }
+        }
+        const float *gi = I + (int64_t)c.n * d.IC * HW + (c.oh0 * d.sH) * d.W + c.ow0 * d.sW;
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int kl = t + 128 * j;
+            if (kl >= len) continue;
+            const int hj = c.oh0 * d.sH + hb[j], wj = c.ow0 * d.sW + wb[j];
+#pragma unroll
+            for (int cc = 0; cc < COLS; cc++) {
+                bool ok = cc < nvalid_cols;
+                if (PADDED)
+                    ok = ok && (unsigned)(hj + (col_hw[cc] >> 16)) < (unsigned)d.H &&
+                         (unsigned)(wj + (col_hw[cc] & 0xFFFF)) < (unsigned)d.W;
+                cp_async_4z(&Bs[cc * GKR_PITCH + kl], ok ? gi + (col_off[cc] + boff[j]) : I, ok);
+            }
+        }
+    };
+    // operand watch of a landed chunk: every staging thread looks at the elements it copied itself
+    auto watch = [&](int stage, const GkChunk &c) {
+        const float *As = gkr_smem + stage * STAGE, *Bs = As + GK_ROWS * GKR_PITCH;
+        const int len = chunk_len(c);
+        if (a16) {
+            const int row = t / 16, l = t % 16;
+#pragma unroll
+            for (int m = 0; m < GKR_KMAX / 64; m++) {
+                const int q = 4 * (l + 16 * m);
+                if (q < len) {
+                    const float4 v = *reinterpret_cast<const float4 *>(&As[row * GKR_PITCH + q]);
+                    unsafe |= cg_unsafe(v.x) | cg_unsafe(v.y) | cg_unsafe(v.z) | cg_unsafe(v.w);
+                }
+            }
+        }
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const int kl = t + 128 * j;
+            if (kl >= len) continue;
+            if (!a16) {
+#pragma unroll
+                for (int row = 0; row < GK_ROWS; row++) unsafe |= cg_unsafe(As[row * GKR_PITCH + kl]);
+            }
+#pragma unroll
+            for (int cc = 0; cc < COLS; cc++) unsafe |= cg_unsafe(Bs[cc * GKR_PITCH + kl]);
+        }
+    };
+
+    // multiplying role: output channel t / 16, columns t % 16 (+ 16 for the second chain)
+    const int crow = t / 16, ccol = t % 16;
+    float acc[CPT];
+#pragma unroll
+    for (int j = 0; j < CPT; j++) acc[j] = 0.0f;
+    // The chains must never wait for shared memory: operands are fetched a group of 16 steps ahead
+    // into a second register set (the loop's trip count is not a constant, so the compiler would not
+    // move the loads of a later iteration above the FMAs of an earlier one by itself).
+    constexpr int G = 4;                     // float4 steps per group
+    constexpr int BJ = 16 * GKR_PITCH / 4;   // float4 distance between a thread's two columns
+    auto multiply = [&](int stage, int len) {
+        const float4 *ar = reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + crow * GKR_PITCH);
+        const float4 *br =
+            reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + (GK_ROWS + ccol) * GKR_PITCH);
+        const int k4 = len >> 2, ng = k4 / G;
+        float4 aA[G], bA[CPT][G], aB[G], bB[CPT][G];
+        auto load = [&](float4 (&a)[G], float4 (&b)[CPT][G], int g) {
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+                a[i] = ar[g * G + i];
+#pragma unroll
+                for (int j = 0; j < CPT; j++) b[j][i] = br[j * BJ + g * G + i];
+            }
+        };
+        auto fma = [&](const float4 (&a)[G], const float4 (&b)[CPT][G]) {
+#pragma unroll
+            for (int i = 0; i < G; i++) {
+#pragma unroll
+                for (int j = 0; j < CPT; j++) {
+                    acc[j] = __fmaf_rn(a[i].x, b[j][i].x, acc[j]);
+                    acc[j] = __fmaf_rn(a[i].y, b[j][i].y, acc[j]);
+                    acc[j] = __fmaf_rn(a[i].z, b[j][i].z, acc[j]);
+                    acc[j] = __fmaf_rn(a[i].w, b[j][i].w, acc[j]);
+                }
+            }
+        };
+        if (ng > 0) load(aA, bA, 0);
+        int g = 0;
+        for (; g + 2 <= ng; g += 2) {
+            load(aB, bB, g + 1);
+            fma(aA, bA);
+            if (g + 2 < ng) load(aA, bA, g + 2);
+            fma(aB, bB);
+        }
+        if (g < ng) fma(aA, bA);
+        for (int i = ng * G; i < k4; i++) {
+            const float4 a = ar[i];
+#pragma unroll
+            for (int j = 0; j < CPT; j++) {
+                const float4 b = br[j * BJ + i];
+                acc[j] = __fmaf_rn(a.x, b.x, acc[j]);
+                acc[j] = __fmaf_rn(a.y, b.y, acc[j]);
+                acc[j] = __fmaf_rn(a.z, b.z, acc[j]);
+                acc[j] = __fmaf_rn(a.w, b.w, acc[j]);
+            }
+        }
+        const float *as = reinterpret_cast<const float *>(ar), *bs = reinterpret_cast<const float *>(br);
+        for (int k = 4 * k4; k < len; k++) {
+#pragma unroll
+            for (int j = 0; j < CPT; j++) acc[j] = __fmaf_rn(as[k], bs[j * 16 * GKR_PITCH + k], acc[j]);
+        }
+    };
+
+    // The two roles run separate loops (so that neither holds the other's registers) and meet at a
+    // named barrier once per chunk: after it chunk ci is visible to all and chunk ci - 1 is done with.
+    auto chunk_barrier = []() { asm volatile("bar.sync 1, %0;" ::"n"(GK_THREADS) : "memory"); };
+    GkChunk cur = {0, 0, 0};
+    int stage = 0;  // stage of chunk ci; the chunk issued in iteration ci goes to the stage before it
+    if (producer) {
+        GkChunk iss = {0, 0, 0};
+#pragma unroll
+        for (int s = 0; s < GKR_STAGES - 1; s++) {
+            if (s < nchunks) issue(s, iss);
+            cp_async_commit();
+            advance(iss);
+        }
+        for (long long ci = 0; ci < nchunks; ci++) {
+            cp_async_wait<GKR_STAGES - 2>();
+            if (PADDED) watch(stage, cur);
+            chunk_barrier();
+            if (ci + GKR_STAGES - 1 < nchunks) issue(stage == 0 ? GKR_STAGES - 1 : stage - 1, iss);
+            cp_async_commit();
+            advance(iss);
+            advance(cur);
+            stage = stage + 1 == GKR_STAGES ? 0 : stage + 1;
+        }
+        cp_async_wait<0>();
+    } else {
+        for (long long ci = 0; ci < nchunks; ci++) {
+            chunk_barrier();
+            multiply(stage, chunk_len(cur));
+            advance(cur);
+            stage = stage + 1 == GKR_STAGES ? 0 : stage + 1;
+        }
+    }
+    const bool redo = PADDED ? (__syncthreads_or(unsafe ? 1 : 0) != 0) : false;
+    const int oc = oc0 + crow;
+    if (!producer && oc < d.OC) {
+#pragma unroll
+        for (int j = 0; j < CPT; j++) {
+            const int col = col0 + ccol + 16 * j;
+            if (col >= ncols) continue;
+            float v = acc[j];
+            if (redo) {
+                const int ic = col / KHW, r = col - ic * KHW;
+                v = conv2d_grad_kernel_exact(GO, I, d, oc, ic, r / d.KW, r % d.KW);
+            }
+            GK[(int64_t)oc * ncols + col] = v;
+        }
+    }
+}
+
+template <int COLS, bool PADDED>
+int launch_gk_rows(const float *go, const float *in, float *gk, const ConvDims &d, int segW, int R,
+                   cudaStream_t st)
+{
+    static unsigned long long done = 0;
+    constexpr int SMEM = GKR_STAGES * (GK_ROWS + COLS) * GKR_PITCH * (int)sizeof(float);
+    int e = ensure_smem(conv_gk_rows_kernel<COLS, PADDED>, SMEM, &done);
+    if (e) return e;
+    const int ncols = d.IC * d.KH * d.KW;
+    const long long nchunks = (long long)d.N * ((d.OH + R - 1) / R) * ((d.OW + segW - 1) / segW);
+    // 16-byte copies of grad_output need every chunk to start on a 16-byte boundary and to hold a
+    // multiple of 4 elements
+    const bool a16 = ((uintptr_t)go % 16 == 0) && ((int64_t)d.OH * d.OW % 4 == 0) &&
+                     (segW == d.OW ? ((int64_t)R * d.OW % 4 == 0) : (d.OW % 4 == 0));
+    dim3 grid((unsigned)((ncols + COLS - 1) / COLS), (unsigned)((d.OC + GK_ROWS - 1) / GK_ROWS));
+    conv_gk_rows_kernel<COLS, PADDED><<<grid, GK_THREADS, SMEM, st>>>(go, in, gk, d, segW, R, a16 ? 1 : 0,
+                                                                     nchunks);
+    return launch_status();
+}
+
 
 int fill_dims(ConvDims &d, int64_t N, int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH,
               int64_t KW, int64_t sH, int64_t sW, int64_t pH, int64_t pW, int64_t groups)
@@ -677,6 +990,19 @@ extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const flo
         const unsigned gy = (unsigned)((d.OC + GK_ROWS - 1) / GK_ROWS);
         // few outputs: one chain per thread spreads them over twice as many SMs
         const bool narrow = (int64_t)((ncols + 31) / 32) * gy < 2 * (int64_t)sm_count();
+        // chunks of whole output rows (of <= 256 columns of a row when rows are longer)
+        const int segW = d.OW <= GKR_KMAX ? d.OW : GKR_KMAX;
+        const int R = d.OW <= GKR_KMAX ? (d.OH < GKR_KMAX / d.OW ? d.OH : GKR_KMAX / d.OW) : 1;
+        if (gy <= 65535 && (int64_t)R * segW >= 64 && d.KH < 32768 && d.KW < 32768 &&
+            (int64_t)d.OH * d.OW < (1 << 30) && ((int64_t)d.H + 2 * d.pH) * d.W < (1 << 30)) {
+            const bool padded = (d.pH | d.pW) != 0;
+            cudaStream_t st = (cudaStream_t)stream;
+            if (narrow)
+                return padded ? launch_gk_rows<16, true>(grad_output, input, grad_kernel, d, segW, R, st)
+                              : launch_gk_rows<16, false>(grad_output, input, grad_kernel, d, segW, R, st);
+            return padded ? launch_gk_rows<32, true>(grad_output, input, grad_kernel, d, segW, R, st)
+                          : launch_gk_rows<32, false>(grad_output, input, grad_kernel, d, segW, R, st);
+        }
         if (gy <= 65535 && d.OW < 65536 && (int64_t)d.OH * d.OW < (1 << 24)) {
             if (narrow)
                 conv_gk_kernel<16><<<dim3((unsigned)((ncols + 15) / 16), gy), GK_THREADS, 0,

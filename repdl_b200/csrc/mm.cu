@@ -333,6 +333,11 @@ int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, 
     if (mid >= 2 * (int64_t)sm_count())
         return launch_one<128, 64, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC,
                                                              st);
+    // Few outputs but a long K (e.g. a 256 x 128 layer output over K = 9216): the time is K times
+    // the instructions one warp issues per k-step, so spread the outputs over more, thinner CTAs.
+    int64_t small = (int64_t)((M + 63) / 64) * ((N + 63) / 64);
+    if (small * 4 <= (int64_t)sm_count() && K >= 1024)
+        return launch_one<32, 32, 4, 4, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
     return launch_one<64, 64, 8, 8, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
 }
 

@@ -176,21 +176,42 @@ chain_sum_kernel(const float *__restrict__ x, float *__restrict__ out, int64_t n
     const int64_t ntiles = (total + CHAIN_TILE - 1) / CHAIN_TILE;
     const int t = threadIdx.x;
 
-    auto stage = [&](int64_t tile, float *dst) {
-        int64_t e0 = tile * CHAIN_TILE;
-#pragma unroll 4
-        for (int i = t; i < CHAIN_TILE; i += CHAIN_THREADS) {
-            int64_t e = e0 + i;
-            float v = 0.0f;
-            if (e < total) {
-                int64_t s = (nseg == 1) ? 0 : e / seglen;
-                int64_t o = e - s * seglen;
-                v = __ldg(base + s * segstride + o);
-            }
-            dst[i] = v;
+    // Warp 0 only walks; warps 1..7 stage.  Each staging thread keeps (segment, offset) of its next
+    // element and advances them by the stride, so no division is needed per element.
+    constexpr int STAGERS = CHAIN_THREADS - 32;
+    const int st = t - 32;  // index among the staging threads (negative in warp 0)
+    int64_t seg = 0, off = 0;
+    if (st >= 0) {
+        seg = (nseg == 1) ? 0 : st / seglen;
+        off = st - seg * seglen;
+    }
+    // bring (seg, off) back to 0 <= off < seglen after off moved by less than a few strides
+    auto renorm = [&]() {
+        if (nseg == 1) return;
+        if (seglen >= STAGERS) {
+            while (off >= seglen) off -= seglen, seg++;
+            while (off < 0) off += seglen, seg--;
+        } else {
+            int64_t q = off / seglen;
+            if (off - q * seglen < 0) q--;
+            seg += q;
+            off -= q * seglen;
         }
     };
-
+    auto stage = [&](int64_t tile, float *dst) {
+        if (st < 0) return;
+        const int64_t e0 = tile * CHAIN_TILE;
+        for (int i = st; i < CHAIN_TILE; i += STAGERS) {
+            dst[i] = (e0 + i < total) ? __ldg(base + seg * segstride + off) : 0.0f;
+            off += STAGERS;
+            renorm();
+        }
+        // This thread has moved ceil((CHAIN_TILE - st) / STAGERS) strides; its first element of the next
+        // tile is CHAIN_TILE after its first element of this one.
+        const int moved = ((CHAIN_TILE - st + STAGERS - 1) / STAGERS) * STAGERS;
+        off += CHAIN_TILE - moved;
+        renorm();
+    };
     float s = 0.0f;
     if (ntiles > 0) stage(0, buf[0]);
     __syncthreads();

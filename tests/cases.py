@@ -78,6 +78,15 @@ def build_cases():
         (2, 32, 12, 12, 64, 3, 3, (1, 1), (1, 1), 1),
         (2, 8, 6, 6, 8, 1, 1, (1, 1), (0, 0), 8),
         (1, 3, 5, 5, 2, 5, 5, (1, 1), (2, 2), 1),
+        # long chains for conv2d_grad_kernel: ragged channel / column counts, row chunks of odd length,
+        # strides with padding, rows wider than one chunk, a 1x1 kernel
+        (5, 5, 15, 13, 11, 3, 3, (1, 1), (0, 0), 1),
+        (4, 7, 17, 19, 9, 3, 3, (2, 2), (1, 1), 1),
+        (3, 3, 20, 23, 10, 5, 3, (1, 2), (2, 0), 1),
+        (1, 2, 3, 300, 3, 2, 3, (1, 1), (0, 1), 1),
+        (2, 2, 4, 530, 5, 3, 3, (1, 2), (1, 1), 1),
+        (6, 20, 10, 10, 12, 1, 1, (1, 1), (0, 0), 1),
+        (3, 4, 16, 16, 8, 3, 3, (1, 1), (1, 1), 1),
     ]
     for ci, (N, IC, H, W, OC, KH, KW, s, p, g) in enumerate(conv_cfgs):
         def mk(N=N, IC=IC, H=H, W=W, OC=OC, KH=KH, KW=KW, s=s, p=p, g=g, ci=ci):
@@ -95,6 +104,28 @@ def build_cases():
                         _randn(600 + ci, N, OC, OH, OW), s, p)
             cases.append(("conv2d_grad_input_%d" % ci, "conv2d_grad_input", mk_gi))
             cases.append(("conv2d_grad_kernel_%d" % ci, "conv2d_grad_kernel", mk_gk))
+
+    # operands that force the exact path of the padded implicit-GEMM forms: an infinity next to zero
+    # padding, and values so small that products vanish (each output meets the infinity at most once,
+    # so no NaN -- whose payload is not part of the contract -- is produced)
+    def unsafe_operands(x_inf=True):
+        x = _randn(470, 3, 4, 16, 16)
+        x.view(-1)[::37] *= 1e-30
+        x.view(-1)[5::91] *= -1e-38
+        if x_inf:
+            x[1, 2, 0, 15] = float("inf")
+        k = _randn(570, 8, 4, 3, 3)
+        k.view(-1)[::13] *= 1e-25
+        go = _randn(670, 3, 8, 16, 16)
+        go.view(-1)[3::29] *= 1e-33
+        go[2, 5, 15, 0] = float("-inf")
+        return x, k, go
+    cases.append(("conv2d_unsafe", "conv2d",
+                  lambda: (unsafe_operands()[0], unsafe_operands()[1], (1, 1), (1, 1), 1)))
+    cases.append(("conv2d_grad_input_unsafe", "conv2d_grad_input",
+                  lambda: ((3, 4, 16, 16), unsafe_operands()[1], unsafe_operands()[2], (1, 1), (1, 1))))
+    cases.append(("conv2d_grad_kernel_unsafe", "conv2d_grad_kernel",
+                  lambda: (unsafe_operands(False)[0], (8, 4, 3, 3), unsafe_operands()[2], (1, 1), (1, 1))))
 
     # ---- sums -----------------------------------------------------------------------------------
     for n in (0, 1, 5, 4095, 4096, 4097, 100000):
