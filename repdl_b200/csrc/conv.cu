@@ -143,7 +143,7 @@ conv2d_grad_kernel_direct_kernel(const float *__restrict__ GO, const float *__re
 // ------------------------------------------------------------------------------------------------
 // exact per-element chains as device functions (the fallback of the GEMM form)
 // ------------------------------------------------------------------------------------------------
-__device__ __forceinline__ float conv2d_exact(const float *__restrict__ I, const float *__restrict__ Kw,
+__device__ __noinline__ float conv2d_exact(const float *__restrict__ I, const float *__restrict__ Kw,
                                               const ConvDims &d, int n, int oc, int oh, int ow)
 {
     const int ICg = d.IC / d.groups, OCg = d.OC / d.groups;
@@ -166,7 +166,7 @@ __device__ __forceinline__ float conv2d_exact(const float *__restrict__ I, const
     return acc;
 }
 
-__device__ __forceinline__ float conv2d_grad_input_exact(const float *__restrict__ GO,
+__device__ __noinline__ float conv2d_grad_input_exact(const float *__restrict__ GO,
                                                          const float *__restrict__ Kw,
                                                          const ConvDims &d, int n, int ic, int h, int w)
 {
@@ -247,6 +247,40 @@ conv_gemm_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, fl
         b_y[j] = p / outW, b_x[j] = p % outW;
         b_base[j] = ((int64_t)n * srcPlanes + (MODE == 0 ? g * ICg : 0)) * srcH * srcW;
     }
+    // Whenever the source position is linear in (kh, kw) -- conv2d at any stride, grad_input at
+    // stride 1 -- an element's address is (a term of the column) + (a term of k), and whether the tap
+    // falls into the padding is one bit of a per-column mask over the KH * KW <= 64 taps; both
+    // column terms are computed once, so an element costs a shift, a test, an add and the load.
+    constexpr bool LIN = MODE == 0 || S1;
+    const float *b_ptr[4];
+    unsigned long long b_mask[4];
+    if (LIN) {
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            const int y0 = MODE == 0 ? b_y[j] * d.sH - d.pH : b_y[j] + d.pH;
+            const int x0 = MODE == 0 ? b_x[j] * d.sW - d.pW : b_x[j] + d.pW;
+            b_ptr[j] = Src + (b_base[j] + (int64_t)y0 * srcW + x0);
+            unsigned long long m = 0;
+            if (b_ok[j]) {
+                for (int kh = 0, r = 0; kh < d.KH; kh++) {
+                    const int sy = MODE == 0 ? y0 + kh : y0 - kh;
+                    for (int kw = 0; kw < d.KW; kw++, r++) {
+                        const int sx = MODE == 0 ? x0 + kw : x0 - kw;
+                        if (sy >= 0 && sy < srcH && sx >= 0 && sx < srcW) m |= 1ull << r;
+                    }
+                }
+            }
+            b_mask[j] = m;
+        }
+    }
+    // k-dependent half of the gather: tap index r and address term of k (LIN only)
+    auto decodeK = [&](int k, int &r, int &kterm) {
+        const int plane = fastdiv(k, d.m40_khw);
+        r = k - plane * KHW;
+        const int kh = fastdiv(r, d.m40_kw), kw = r - kh * d.KW;
+        const int tap = kh * srcW + kw;
+        kterm = plane * srcH * srcW + (MODE == 0 ? tap : -tap);
+    };
     auto gatherB = [&](int k, int j) -> float {
         if (k >= K || !b_ok[j]) return 0.0f;
         const int plane = fastdiv(k, d.m40_khw), r = k - plane * KHW;
@@ -259,13 +293,8 @@ conv_gemm_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, fl
         } else {
             const int nh = b_y[j] + d.pH - kh, nw = b_x[j] + d.pW - kw;
             if (nh < 0 || nw < 0) return 0.0f;
-            if (S1) {
-                sy = nh, sx = nw;
-                if (sy >= srcH || sx >= srcW) return 0.0f;
-            } else {
-                sy = nh / d.sH, sx = nw / d.sW;
-                if (sy >= srcH || sx >= srcW || sy * d.sH != nh || sx * d.sW != nw) return 0.0f;
-            }
+            sy = nh / d.sH, sx = nw / d.sW;
+            if (sy >= srcH || sx >= srcW || sy * d.sH != nh || sx * d.sW != nw) return 0.0f;
         }
         return __ldg(Src + b_base[j] + ((int64_t)plane * srcH + sy) * srcW + sx);
     };
@@ -294,10 +323,21 @@ conv_gemm_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, fl
 #pragma unroll
         for (int i = 0; i < NVB; i++) {
             const int k = k0 + bk0 + (NT / (CG_BN / 4)) * i;
+            if (LIN) {
+                int r = 0, kterm = 0;
+                if (k < K) decodeK(k, r, kterm);
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                bv[i][j] = gatherB(k, j);
-                unsafe |= cg_unsafe(bv[i][j]);
+                for (int j = 0; j < 4; j++) {
+                    const bool ok = k < K && ((b_mask[j] >> r) & 1ull) != 0;
+                    bv[i][j] = ok ? __ldg(b_ptr[j] + kterm) : 0.0f;
+                    unsafe |= cg_unsafe(bv[i][j]);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    bv[i][j] = gatherB(k, j);
+                    unsafe |= cg_unsafe(bv[i][j]);
+                }
             }
         }
     };
@@ -605,31 +645,31 @@ conv_gk_kernel(const float *__restrict__ GO, const float *__restrict__ I, float 
 
 // ------------------------------------------------------------------------------------------------
 // conv2d_grad_kernel, row-chunk form (the one used whenever an image's output rows give chunks of a
-// useful length).  Same split of roles as above -- 4 warps that only multiply, one chain per thread
-// and column, and 4 warps that only stage -- but the staging warps never touch a value: k is walked
-// image by image in chunks of R whole output rows (or of <= 256 columns of one row when rows are
-// longer than that), every operand element goes global -> shared with one 4-byte cp.async (16-byte
-// for grad_output when its rows allow it), three chunks are in flight, and the (row, column) decoding
-// of a thread's elements is the same for every chunk, so it is done once.  What is left per element
-// is an integer add, the address and the copy.  Padding taps and the ragged ends are zero-filled by
-// the copy itself (src-size 0), so only a padded convolution needs the operand watch: there the
-// staging threads read back what they copied when it has landed, and the CTA falls back to the exact
-// loop for its outputs if a non-finite or vanishing value was seen.
+// useful length).  Same split of roles as above -- warps that only multiply, one chain per thread, and
+// 8 warps that only stage -- but the staging warps never touch a value: k is walked image by image in
+// chunks of R whole output rows (or of <= 256 columns of one row when rows are longer than that),
+// every operand element goes global -> shared with one 4-byte cp.async (16-byte for grad_output when
+// its rows allow it), three chunks are in flight, and the (row, column) decoding of a thread's
+// elements is the same for every chunk, so it is done once.  What is left per element is the address
+// and the copy.  Padding taps are zero-filled by the copy itself (src-size 0), so only a padded
+// convolution needs the operand watch: there the staging threads read back what they copied when it
+// has landed, and the CTA falls back to the exact loop for its outputs if a non-finite or vanishing
+// value was seen.  A CTA's tile is 8 output channels x 16 weight columns (4 multiplying warps), or
+// 4 x 8 (one warp) when there are so few outputs that the larger tile would leave most SMs idle.
 // ------------------------------------------------------------------------------------------------
 constexpr int GKR_KMAX = 256, GKR_PITCH = GKR_KMAX + 4, GKR_STAGES = 3;
+constexpr int GKR_STAGERS = 256;  // staging threads (8 warps)
 
+__device__ __forceinline__ void cp_async_4(float *smem_dst, const float *gmem_src)
+{
+    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"(dst), "l"(gmem_src) : "memory");
+}
 __device__ __forceinline__ void cp_async_4z(float *smem_dst, const float *gmem_src, bool ok)
 {
     const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
     const int bytes = ok ? 4 : 0;  // 0: nothing is read, the word is zero-filled
     asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes)
-                 : "memory");
-}
-__device__ __forceinline__ void cp_async_16z(float *smem_dst, const float *gmem_src, bool ok)
-{
-    const unsigned dst = (unsigned)__cvta_generic_to_shared(smem_dst);
-    const int bytes = ok ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(gmem_src), "r"(bytes)
                  : "memory");
 }
 
@@ -638,19 +678,21 @@ struct GkChunk {
     int n, oh0, ow0;
 };
 
-template <int COLS, bool PADDED>
-__global__ void __launch_bounds__(GK_THREADS)
+// RW x CB multiplying warps, each owning a patch of 4 output channels x 8 weight columns.
+template <bool PADDED, int RW, int CB>
+__global__ void __launch_bounds__((RW * CB) * 32 + GKR_STAGERS)
 conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, float *__restrict__ GK,
                     ConvDims d, int segW, int R, int a16, long long nchunks)
 {
     extern __shared__ __align__(16) float gkr_smem[];
-    constexpr int STAGE = (GK_ROWS + COLS) * GKR_PITCH;
-    constexpr int CPT = COLS / 16;
-    const bool producer = threadIdx.x >= 128;
-    const int t = threadIdx.x & 127;
+    constexpr int ROWS = 4 * RW, COLS = 8 * CB, NCW = RW * CB;
+    constexpr int NT = NCW * 32 + GKR_STAGERS;
+    constexpr int STAGE = (ROWS + COLS) * GKR_PITCH;
+    const bool producer = threadIdx.x >= NCW * 32;
+    const int t = producer ? threadIdx.x - NCW * 32 : threadIdx.x;  // index within the role
     const int KHW = d.KH * d.KW, OHW = d.OH * d.OW, HW = d.H * d.W;
     const int ncols = d.IC * KHW;
-    const int oc0 = blockIdx.y * GK_ROWS, col0 = blockIdx.x * COLS;
+    const int oc0 = blockIdx.y * ROWS, col0 = blockIdx.x * COLS;
 
     auto chunk_len = [&](const GkChunk &c) {
         const int rows = min(R, d.OH - c.oh0);
@@ -664,167 +706,101 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
             if (c.oh0 >= d.OH) c.oh0 = 0, c.n++;
         }
     };
-
-    // staging role: this thread's elements of a chunk are k_local = t and t + 128 of every row and column
-    int boff[2], hb[2], wb[2];
-#pragma unroll
-    for (int j = 0; j < 2; j++) {
-        const int kl = t + 128 * j;
-        const int r = kl / segW, c = kl - r * segW;
-        boff[j] = r * d.sH * d.W + c * d.sW;
-        hb[j] = r * d.sH - d.pH;
-        wb[j] = c * d.sW - d.pW;
-    }
-    int col_off[COLS], col_hw[COLS];
-#pragma unroll
-    for (int c = 0; c < COLS; c++) {
-        const int col = min(col0 + c, ncols - 1);
-        const int ic = col / KHW, r = col - ic * KHW;
-        const int kh = r / d.KW, kw = r - kh * d.KW;
-        col_off[c] = ic * HW + (kh - d.pH) * d.W + (kw - d.pW);
-        col_hw[c] = (kh << 16) | kw;
-    }
-    const int nvalid_cols = ncols - col0;
-    bool unsafe = false;
-
-    auto issue = [&](int stage, const GkChunk &c) {
-        float *As = gkr_smem + stage * STAGE, *Bs = As + GK_ROWS * GKR_PITCH;
-        const int len = chunk_len(c);
-        const float *ga = GO + ((int64_t)c.n * d.OC + oc0) * OHW + c.oh0 * d.OW + c.ow0;
-        if (a16) {
-            const int row = t / 16, l = t % 16;
-            const bool ok = oc0 + row < d.OC;
-            const float *src = ok ? ga + (int64_t)row * OHW : GO;
-#pragma unroll
-            for (int m = 0; m < GKR_KMAX / 64; m++) {
-                const int q = 4 * (l + 16 * m);
-                if (q < len) cp_async_16z(&As[row * GKR_PITCH + q], ok ? src + q : GO, ok);
-            }
-        } else {
-#pragma unroll
-            for (int j = 0; j < 2; j++) {
-                const int kl = t + 128 * j;
-                if (kl >= len) continue;
-#pragma unroll
-                for (int row = 0; row < GK_ROWS; row++) {
-                    const bool ok = oc0 + row < d.OC;
-                    cp_async_4z(&As[row * GKR_PITCH + kl], ok ? ga + (int64_t)row * OHW + kl : GO, ok);
-                }
-            }
-        }
-        const float *gi = I + (int64_t)c.n * d.IC * HW + (c.oh0 * d.sH) * d.W + c.ow0 * d.sW;
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int kl = t + 128 * j;
-            if (kl >= len) continue;
-            const int hj = c.oh0 * d.sH + hb[j], wj = c.ow0 * d.sW + wb[j];
-#pragma unroll
-            for (int cc = 0; cc < COLS; cc++) {
-                bool ok = cc < nvalid_cols;
-                if (PADDED)
-                    ok = ok && (unsigned)(hj + (col_hw[cc] >> 16)) < (unsigned)d.H &&
-                         (unsigned)(wj + (col_hw[cc] & 0xFFFF)) < (unsigned)d.W;
-                cp_async_4z(&Bs[cc * GKR_PITCH + kl], ok ? gi + (col_off[cc] + boff[j]) : I, ok);
-            }
-        }
-    };
-    // operand watch of a landed chunk: every staging thread looks at the elements it copied itself
-    auto watch = [&](int stage, const GkChunk &c) {
-        const float *As = gkr_smem + stage * STAGE, *Bs = As + GK_ROWS * GKR_PITCH;
-        const int len = chunk_len(c);
-        if (a16) {
-            const int row = t / 16, l = t % 16;
-#pragma unroll
-            for (int m = 0; m < GKR_KMAX / 64; m++) {
-                const int q = 4 * (l + 16 * m);
-                if (q < len) {
-                    const float4 v = *reinterpret_cast<const float4 *>(&As[row * GKR_PITCH + q]);
-                    unsafe |= cg_unsafe(v.x) | cg_unsafe(v.y) | cg_unsafe(v.z) | cg_unsafe(v.w);
-                }
-            }
-        }
-#pragma unroll
-        for (int j = 0; j < 2; j++) {
-            const int kl = t + 128 * j;
-            if (kl >= len) continue;
-            if (!a16) {
-#pragma unroll
-                for (int row = 0; row < GK_ROWS; row++) unsafe |= cg_unsafe(As[row * GKR_PITCH + kl]);
-            }
-#pragma unroll
-            for (int cc = 0; cc < COLS; cc++) unsafe |= cg_unsafe(Bs[cc * GKR_PITCH + kl]);
-        }
-    };
-
-    // multiplying role: output channel t / 16, columns t % 16 (+ 16 for the second chain)
-    const int crow = t / 16, ccol = t % 16;
-    float acc[CPT];
-#pragma unroll
-    for (int j = 0; j < CPT; j++) acc[j] = 0.0f;
-    // The chains must never wait for shared memory: operands are fetched a group of 16 steps ahead
-    // into a second register set (the loop's trip count is not a constant, so the compiler would not
-    // move the loads of a later iteration above the FMAs of an earlier one by itself).
-    constexpr int G = 4;                     // float4 steps per group
-    constexpr int BJ = 16 * GKR_PITCH / 4;   // float4 distance between a thread's two columns
-    auto multiply = [&](int stage, int len) {
-        const float4 *ar = reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + crow * GKR_PITCH);
-        const float4 *br =
-            reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + (GK_ROWS + ccol) * GKR_PITCH);
-        const int k4 = len >> 2, ng = k4 / G;
-        float4 aA[G], bA[CPT][G], aB[G], bB[CPT][G];
-        auto load = [&](float4 (&a)[G], float4 (&b)[CPT][G], int g) {
-#pragma unroll
-            for (int i = 0; i < G; i++) {
-                a[i] = ar[g * G + i];
-#pragma unroll
-                for (int j = 0; j < CPT; j++) b[j][i] = br[j * BJ + g * G + i];
-            }
-        };
-        auto fma = [&](const float4 (&a)[G], const float4 (&b)[CPT][G]) {
-#pragma unroll
-            for (int i = 0; i < G; i++) {
-#pragma unroll
-                for (int j = 0; j < CPT; j++) {
-                    acc[j] = __fmaf_rn(a[i].x, b[j][i].x, acc[j]);
-                    acc[j] = __fmaf_rn(a[i].y, b[j][i].y, acc[j]);
-                    acc[j] = __fmaf_rn(a[i].z, b[j][i].z, acc[j]);
-                    acc[j] = __fmaf_rn(a[i].w, b[j][i].w, acc[j]);
-                }
-            }
-        };
-        if (ng > 0) load(aA, bA, 0);
-        int g = 0;
-        for (; g + 2 <= ng; g += 2) {
-            load(aB, bB, g + 1);
-            fma(aA, bA);
-            if (g + 2 < ng) load(aA, bA, g + 2);
-            fma(aB, bB);
-        }
-        if (g < ng) fma(aA, bA);
-        for (int i = ng * G; i < k4; i++) {
-            const float4 a = ar[i];
-#pragma unroll
-            for (int j = 0; j < CPT; j++) {
-                const float4 b = br[j * BJ + i];
-                acc[j] = __fmaf_rn(a.x, b.x, acc[j]);
-                acc[j] = __fmaf_rn(a.y, b.y, acc[j]);
-                acc[j] = __fmaf_rn(a.z, b.z, acc[j]);
-                acc[j] = __fmaf_rn(a.w, b.w, acc[j]);
-            }
-        }
-        const float *as = reinterpret_cast<const float *>(ar), *bs = reinterpret_cast<const float *>(br);
-        for (int k = 4 * k4; k < len; k++) {
-#pragma unroll
-            for (int j = 0; j < CPT; j++) acc[j] = __fmaf_rn(as[k], bs[j * 16 * GKR_PITCH + k], acc[j]);
-        }
-    };
-
     // The two roles run separate loops (so that neither holds the other's registers) and meet at a
     // named barrier once per chunk: after it chunk ci is visible to all and chunk ci - 1 is done with.
-    auto chunk_barrier = []() { asm volatile("bar.sync 1, %0;" ::"n"(GK_THREADS) : "memory"); };
+    auto chunk_barrier = []() { asm volatile("bar.sync 1, %0;" ::"n"(NT) : "memory"); };
     GkChunk cur = {0, 0, 0};
     int stage = 0;  // stage of chunk ci; the chunk issued in iteration ci goes to the stage before it
+    bool unsafe = false;
+    float acc = 0.0f;
+    // Multiplying role: which output of the CTA's tile a thread owns.  Shared memory serves a 16-byte
+    // load eight lanes at a time, and passes of one load that fetch the same addresses in the same
+    // lanes are merged.  So the lanes of a warp's 4 x 8 patch are laid out with all four rows in
+    // every group of eight lanes (the row operand then costs one pass instead of four) and two of
+    // the eight columns per group.
+    const int cw = t / 32, lane = t % 32;
+    const int prow = (lane % 8) / 2, pcol = 2 * (lane / 8) + lane % 2;
+    const int crow = 4 * (cw / CB) + prow, ccol = 8 * (cw % CB) + pcol;
+
     if (producer) {
+        // Thread t copies step k_local = t of every row and column of a chunk.  Rows and columns past
+        // the end are clamped to the last valid one: they are copied twice and feed outputs nobody
+        // stores, which is cheaper than predicating every copy.
+        const int sr = t / segW, sc = t - sr * segW;
+        const int boff = sr * d.sH * d.W + sc * d.sW;
+        const int hb = sr * d.sH - d.pH, wb = sc * d.sW - d.pW;
+        int col_off[COLS], col_hw[COLS];
+#pragma unroll
+        for (int c = 0; c < COLS; c++) {
+            const int col = min(col0 + c, ncols - 1);
+            const int ic = col / KHW, r = col - ic * KHW;
+            const int kh = r / d.KW, kw = r - kh * d.KW;
+            col_off[c] = ic * HW + (kh - d.pH) * d.W + (kw - d.pW);
+            col_hw[c] = (kh << 16) | kw;
+        }
+        // 16-byte copies of grad_output: LPR threads per row, along k
+        constexpr int LPR = GKR_STAGERS / ROWS, A16M = (GKR_KMAX / 4 + LPR - 1) / LPR;
+        const int a16r = t / LPR, a16l = t % LPR;
+        const int a16src = min(oc0 + a16r, d.OC - 1) - oc0;
+
+        auto issue = [&](int st, const GkChunk &c) {
+            float *As = gkr_smem + st * STAGE, *Bs = As + ROWS * GKR_PITCH;
+            const int len = chunk_len(c);
+            const float *ga = GO + ((int64_t)c.n * d.OC + oc0) * OHW + c.oh0 * d.OW + c.ow0;
+            if (a16) {
+                const float *src = ga + (int64_t)a16src * OHW;
+#pragma unroll
+                for (int m = 0; m < A16M; m++) {
+                    const int q = 4 * (a16l + LPR * m);
+                    if (q < len) cp_async_16(&As[a16r * GKR_PITCH + q], src + q);
+                }
+            } else if (t < len) {
+#pragma unroll
+                for (int row = 0; row < ROWS; row++) {
+                    const int rr = min(oc0 + row, d.OC - 1) - oc0;
+                    cp_async_4(&As[row * GKR_PITCH + t], ga + (int64_t)rr * OHW + t);
+                }
+            }
+            if (t < len) {
+                const float *gi =
+                    I + ((int64_t)c.n * d.IC * HW + (c.oh0 * d.sH) * d.W + c.ow0 * d.sW + boff);
+                const int hj = c.oh0 * d.sH + hb, wj = c.ow0 * d.sW + wb;
+#pragma unroll
+                for (int cc = 0; cc < COLS; cc++) {
+                    if (PADDED) {
+                        const bool ok = (unsigned)(hj + (col_hw[cc] >> 16)) < (unsigned)d.H &&
+                                        (unsigned)(wj + (col_hw[cc] & 0xFFFF)) < (unsigned)d.W;
+                        cp_async_4z(&Bs[cc * GKR_PITCH + t], ok ? gi + col_off[cc] : I, ok);
+                    } else {
+                        cp_async_4(&Bs[cc * GKR_PITCH + t], gi + col_off[cc]);
+                    }
+                }
+            }
+        };
+        // operand watch of a landed chunk: every staging thread looks at the elements it copied itself
+        auto watch = [&](int st, const GkChunk &c) {
+            const float *As = gkr_smem + st * STAGE, *Bs = As + ROWS * GKR_PITCH;
+            const int len = chunk_len(c);
+            if (a16) {
+#pragma unroll
+                for (int m = 0; m < A16M; m++) {
+                    const int q = 4 * (a16l + LPR * m);
+                    if (q < len) {
+                        const float4 v = *reinterpret_cast<const float4 *>(&As[a16r * GKR_PITCH + q]);
+                        unsafe |= cg_unsafe(v.x) | cg_unsafe(v.y) | cg_unsafe(v.z) | cg_unsafe(v.w);
+                    }
+                }
+            }
+            if (t < len) {
+                if (!a16) {
+#pragma unroll
+                    for (int row = 0; row < ROWS; row++) unsafe |= cg_unsafe(As[row * GKR_PITCH + t]);
+                }
+#pragma unroll
+                for (int cc = 0; cc < COLS; cc++) unsafe |= cg_unsafe(Bs[cc * GKR_PITCH + t]);
+            }
+        };
+
         GkChunk iss = {0, 0, 0};
 #pragma unroll
         for (int s = 0; s < GKR_STAGES - 1; s++) {
@@ -844,6 +820,50 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
         }
         cp_async_wait<0>();
     } else {
+        // Operands are fetched a group of 8 steps ahead into a second register set (the loop's trip
+        // count is not a constant, so the compiler would not move the loads of a later iteration above
+        // the FMAs of an earlier one by itself).  Measured on B200: a warp spends about 4 cycles per
+        // step on the dependent FMA and about 4 more on its two 16-byte shared-memory loads per four
+        // steps, whose passes do not overlap with the warp's own FMAs; longer groups were slower.
+        constexpr int G = 2;  // float4 steps per group
+        auto multiply = [&](int st, int len) {
+            const float4 *ar = reinterpret_cast<const float4 *>(gkr_smem + st * STAGE + crow * GKR_PITCH);
+            const float4 *br =
+                reinterpret_cast<const float4 *>(gkr_smem + st * STAGE + (ROWS + ccol) * GKR_PITCH);
+            const int k4 = len >> 2, ng = k4 / G;
+            float4 aA[G], bA[G], aB[G], bB[G];
+            auto load = [&](float4 (&a)[G], float4 (&b)[G], int g) {
+#pragma unroll
+                for (int i = 0; i < G; i++) a[i] = ar[g * G + i], b[i] = br[g * G + i];
+            };
+            auto fma = [&](const float4 (&a)[G], const float4 (&b)[G]) {
+#pragma unroll
+                for (int i = 0; i < G; i++) {
+                    acc = __fmaf_rn(a[i].x, b[i].x, acc);
+                    acc = __fmaf_rn(a[i].y, b[i].y, acc);
+                    acc = __fmaf_rn(a[i].z, b[i].z, acc);
+                    acc = __fmaf_rn(a[i].w, b[i].w, acc);
+                }
+            };
+            if (ng > 0) load(aA, bA, 0);
+            int g = 0;
+            for (; g + 2 <= ng; g += 2) {
+                load(aB, bB, g + 1);
+                fma(aA, bA);
+                if (g + 2 < ng) load(aA, bA, g + 2);
+                fma(aB, bB);
+            }
+            if (g < ng) fma(aA, bA);
+            for (int i = ng * G; i < k4; i++) {
+                const float4 a = ar[i], b = br[i];
+                acc = __fmaf_rn(a.x, b.x, acc);
+                acc = __fmaf_rn(a.y, b.y, acc);
+                acc = __fmaf_rn(a.z, b.z, acc);
+                acc = __fmaf_rn(a.w, b.w, acc);
+            }
+            const float *as = reinterpret_cast<const float *>(ar), *bs = reinterpret_cast<const float *>(br);
+            for (int k = 4 * k4; k < len; k++) acc = __fmaf_rn(as[k], bs[k], acc);
+        };
         for (long long ci = 0; ci < nchunks; ci++) {
             chunk_barrier();
             multiply(stage, chunk_len(cur));
@@ -852,13 +872,10 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
         }
     }
     const bool redo = PADDED ? (__syncthreads_or(unsafe ? 1 : 0) != 0) : false;
-    const int oc = oc0 + crow;
-    if (!producer && oc < d.OC) {
-#pragma unroll
-        for (int j = 0; j < CPT; j++) {
-            const int col = col0 + ccol + 16 * j;
-            if (col >= ncols) continue;
-            float v = acc[j];
+    if (!producer) {
+        const int oc = oc0 + crow, col = col0 + ccol;
+        if (oc < d.OC && col < ncols) {
+            float v = acc;
             if (redo) {
                 const int ic = col / KHW, r = col - ic * KHW;
                 v = conv2d_grad_kernel_exact(GO, I, d, oc, ic, r / d.KW, r % d.KW);
@@ -868,13 +885,14 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
     }
 }
 
-template <int COLS, bool PADDED>
+template <bool PADDED, int RW, int CB>
 int launch_gk_rows(const float *go, const float *in, float *gk, const ConvDims &d, int segW, int R,
                    cudaStream_t st)
 {
     static unsigned long long done = 0;
-    constexpr int SMEM = GKR_STAGES * (GK_ROWS + COLS) * GKR_PITCH * (int)sizeof(float);
-    int e = ensure_smem(conv_gk_rows_kernel<COLS, PADDED>, SMEM, &done);
+    constexpr int ROWS = 4 * RW, COLS = 8 * CB;
+    constexpr int SMEM = GKR_STAGES * (ROWS + COLS) * GKR_PITCH * (int)sizeof(float);
+    int e = ensure_smem(conv_gk_rows_kernel<PADDED, RW, CB>, SMEM, &done);
     if (e) return e;
     const int ncols = d.IC * d.KH * d.KW;
     const long long nchunks = (long long)d.N * ((d.OH + R - 1) / R) * ((d.OW + segW - 1) / segW);
@@ -882,10 +900,24 @@ int launch_gk_rows(const float *go, const float *in, float *gk, const ConvDims &
     // multiple of 4 elements
     const bool a16 = ((uintptr_t)go % 16 == 0) && ((int64_t)d.OH * d.OW % 4 == 0) &&
                      (segW == d.OW ? ((int64_t)R * d.OW % 4 == 0) : (d.OW % 4 == 0));
-    dim3 grid((unsigned)((ncols + COLS - 1) / COLS), (unsigned)((d.OC + GK_ROWS - 1) / GK_ROWS));
-    conv_gk_rows_kernel<COLS, PADDED><<<grid, GK_THREADS, SMEM, st>>>(go, in, gk, d, segW, R, a16 ? 1 : 0,
-                                                                     nchunks);
+    dim3 grid((unsigned)((ncols + COLS - 1) / COLS), (unsigned)((d.OC + ROWS - 1) / ROWS));
+    conv_gk_rows_kernel<PADDED, RW, CB><<<grid, RW * CB * 32 + GKR_STAGERS, SMEM, st>>>(
+        go, in, gk, d, segW, R, a16 ? 1 : 0, nchunks);
     return launch_status();
+}
+
+// few outputs: patches of 4 x 8 (one multiplying warp per CTA) put them on four times as many SMs
+int launch_gk_rows_any(const float *go, const float *in, float *gk, const ConvDims &d, int segW, int R,
+                       cudaStream_t st)
+{
+    const int ncols = d.IC * d.KH * d.KW;
+    const bool padded = (d.pH | d.pW) != 0;
+    const int64_t big_tiles = (int64_t)((ncols + 15) / 16) * ((d.OC + 7) / 8);
+    if (2 * big_tiles < sm_count())
+        return padded ? launch_gk_rows<true, 1, 1>(go, in, gk, d, segW, R, st)
+                      : launch_gk_rows<false, 1, 1>(go, in, gk, d, segW, R, st);
+    return padded ? launch_gk_rows<true, 2, 2>(go, in, gk, d, segW, R, st)
+                  : launch_gk_rows<false, 2, 2>(go, in, gk, d, segW, R, st);
 }
 
 
@@ -992,16 +1024,17 @@ extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const flo
         const bool narrow = (int64_t)((ncols + 31) / 32) * gy < 2 * (int64_t)sm_count();
         // chunks of whole output rows (of <= 256 columns of a row when rows are longer)
         const int segW = d.OW <= GKR_KMAX ? d.OW : GKR_KMAX;
-        const int R = d.OW <= GKR_KMAX ? (d.OH < GKR_KMAX / d.OW ? d.OH : GKR_KMAX / d.OW) : 1;
-        if (gy <= 65535 && (int64_t)R * segW >= 64 && d.KH < 32768 && d.KW < 32768 &&
+        int R = d.OW <= GKR_KMAX ? (d.OH < GKR_KMAX / d.OW ? d.OH : GKR_KMAX / d.OW) : 1;
+        // prefer a chunk length that is a whole number of 8-step operand groups, if that costs
+        // less than half the chunk
+        for (int r = R; 2 * r > R; r--)
+            if ((int64_t)r * d.OW % 8 == 0) {
+                R = r;
+                break;
+            }
+        if ((d.OC + 3) / 4 <= 65535 && (int64_t)R * segW >= 64 && d.KH < 32768 && d.KW < 32768 &&
             (int64_t)d.OH * d.OW < (1 << 30) && ((int64_t)d.H + 2 * d.pH) * d.W < (1 << 30)) {
-            const bool padded = (d.pH | d.pW) != 0;
-            cudaStream_t st = (cudaStream_t)stream;
-            if (narrow)
-                return padded ? launch_gk_rows<16, true>(grad_output, input, grad_kernel, d, segW, R, st)
-                              : launch_gk_rows<16, false>(grad_output, input, grad_kernel, d, segW, R, st);
-            return padded ? launch_gk_rows<32, true>(grad_output, input, grad_kernel, d, segW, R, st)
-                          : launch_gk_rows<32, false>(grad_output, input, grad_kernel, d, segW, R, st);
+            return launch_gk_rows_any(grad_output, input, grad_kernel, d, segW, R, (cudaStream_t)stream);
         }
         if (gy <= 65535 && d.OW < 65536 && (int64_t)d.OH * d.OW < (1 << 24)) {
             if (narrow)
