@@ -161,7 +161,7 @@ struct OutSet {
 #endif
 constexpr bool kF2 = REPDL_MM_F2 != 0;
 
-template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB>
+template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB, int D>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB)
 sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const OutSet out, int M,
              int N, int K, int64_t lda, int64_t ldb, int64_t ldc, int tilesM, int tilesN, int vecC)
@@ -194,21 +194,34 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
         for (int j = 0; j < TN / 2; j++) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
     }
 
-    LoadA la;
-    LoadB lb;
+    // D register sets hold the slabs kt + 1 .. kt + D on their way from global to shared memory.
+    // D = 1 is the plain double buffer; a small tile with a long K cannot cover the L2 / HBM latency
+    // with the arithmetic of one slab and few CTAs are resident, so it keeps D = 4 slabs in flight.
+    LoadA la[D];
+    LoadB lb[D];
     const int nk = (K + BK - 1) / BK;
-    la.load(A, lda, m0, 0, M, K, -0.0f, t);
-    lb.load(B, ldb, n0, 0, N, K, 0.0f, t);
-    la.store(As[0], t);
-    lb.store(Bs[0], t);
+#pragma unroll
+    for (int s = 0; s < D; s++) {
+        if (s < nk) {
+            la[s].load(A, lda, m0, s * BK, M, K, -0.0f, t);
+            lb[s].load(B, ldb, n0, s * BK, N, K, 0.0f, t);
+        }
+    }
+    la[0].store(As[0], t);
+    lb[0].store(Bs[0], t);
     __syncthreads();
 
-    for (int kt = 0; kt < nk; kt++) {
+    for (int kt0 = 0; kt0 < nk; kt0 += D) {
+#pragma unroll
+      for (int s = 0; s < D; s++) {
+        const int kt = kt0 + s;
+        if (kt >= nk) break;
         const int cur = kt & 1;
         const bool more = kt + 1 < nk;
-        if (more) {
-            la.load(A, lda, m0, (kt + 1) * BK, M, K, -0.0f, t);
-            lb.load(B, ldb, n0, (kt + 1) * BK, N, K, 0.0f, t);
+        // slab kt already sits in shared memory, so its register set takes slab kt + D
+        if (kt + D < nk) {
+            la[s].load(A, lda, m0, (kt + D) * BK, M, K, -0.0f, t);
+            lb[s].load(B, ldb, n0, (kt + D) * BK, N, K, 0.0f, t);
         }
         REPDL_UNROLL(REPDL_MM_KUNROLL)
         for (int k = 0; k < BK; k++) {
@@ -258,10 +271,11 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
             }
         }
         if (more) {
-            la.store(As[cur ^ 1], t);
-            lb.store(Bs[cur ^ 1], t);
+            la[(s + 1) % D].store(As[cur ^ 1], t);
+            lb[(s + 1) % D].store(Bs[cur ^ 1], t);
         }
         __syncthreads();
+      }
     }
 
 #pragma unroll
@@ -294,14 +308,14 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
     }
 }
 
-template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB>
+template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB, int D = 1>
 int launch_one(const float *A, const float *B, const OutSet &C, int M, int N, int K, int64_t lda,
                int64_t ldb, int64_t ldc, int vecC, cudaStream_t st)
 {
     int tilesM = (M + BM - 1) / BM, tilesN = (N + BN - 1) / BN;
     int64_t tiles = (int64_t)tilesM * tilesN;
     if (tiles > 0x7FFFFFFF) return REPDL_E_RANGE;
-    auto kern = sgemm_kernel<BM, BN, TM, TN, A_KC, B_KC, VEC, MINB>;
+    auto kern = sgemm_kernel<BM, BN, TM, TN, A_KC, B_KC, VEC, MINB, D>;
     constexpr int smem_bytes = 2 * BK * ((kF2 ? 2 : 1) * BM + 4 + BN + 4) * (int)sizeof(float);
     static unsigned long long smem_done = 0;  // one mask per kernel instantiation
     int e = ensure_smem(kern, smem_bytes, &smem_done);
@@ -337,7 +351,7 @@ int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, 
     // the instructions one warp issues per k-step, so spread the outputs over more, thinner CTAs.
     int64_t small = (int64_t)((M + 63) / 64) * ((N + 63) / 64);
     if (small * 4 <= (int64_t)sm_count() && K >= 1024)
-        return launch_one<32, 32, 4, 4, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
+        return launch_one<32, 32, 4, 4, A_KC, B_KC, VEC, 8, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
     return launch_one<64, 64, 8, 8, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
 }
 

@@ -15,6 +15,45 @@ import torch
 from . import ops
 
 
+# Side streams for operator calls of one backward pass that do not depend on each other, per device.
+_side = {}
+
+
+def _concurrently(*thunks):
+    """Launches each thunk (one operator call returning one tensor, or None) so that they may overlap.
+
+    The weight gradient of a convolution is a few thousand long dependent FMA chains and the bias
+    gradient a few dozen even longer add chains: both are bound by instruction latency and leave most
+    of the GPU idle, and neither depends on the other or on the input gradient.  The first thunk runs
+    on the current stream, the others on side streams that start after everything already queued on
+    the current stream; the current stream then waits for them, so callers see ordinary stream
+    semantics.  Every operator is deterministic on its own, so the bits do not depend on the overlap.
+    """
+    live = [i for i, t in enumerate(thunks) if t is not None]
+    out = [None] * len(thunks)
+    if len(live) <= 1:
+        for i in live:
+            out[i] = thunks[i]()
+        return out
+    main = torch.cuda.current_stream()
+    key = (main.device.index, main.cuda_stream)
+    slots = _side.setdefault(key, [])
+    while len(slots) < len(live) - 1:
+        slots.append((torch.cuda.Stream(device=main.device), torch.cuda.Event(), torch.cuda.Event()))
+    ready = slots[0][1]
+    ready.record(main)
+    out[live[0]] = thunks[live[0]]()
+    for (stream, _, done), i in zip(slots, live[1:]):
+        stream.wait_event(ready)
+        with torch.cuda.stream(stream):
+            out[i] = thunks[i]()
+        out[i].record_stream(main)   # allocated from the side stream's pool, consumed on the main one
+        done.record(stream)
+    for (_, _, done), _ in zip(slots, live[1:]):
+        main.wait_event(done)
+    return out
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -64,13 +103,11 @@ class _Conv2d(torch.autograd.Function):
         if groups != 1:
             raise NotImplementedError("grouped convolution has no backward (as in the reference)")
         x, weight = ctx.saved_tensors
-        gx = gw = gb = None
-        if ctx.needs_input_grad[0]:
-            gx = ops.conv2d_grad_input(x.shape, weight, g, stride, padding)
-        if ctx.needs_input_grad[1]:
-            gw = ops.conv2d_grad_kernel(x, weight.shape, g, stride, padding)
-        if ctx.needs_input_grad[2]:
-            gb = ops.sum4d_dim023(g)
+        need = ctx.needs_input_grad
+        gw, gb, gx = _concurrently(
+            (lambda: ops.conv2d_grad_kernel(x, weight.shape, g, stride, padding)) if need[1] else None,
+            (lambda: ops.sum4d_dim023(g)) if need[2] else None,
+            (lambda: ops.conv2d_grad_input(x.shape, weight, g, stride, padding)) if need[0] else None)
         return gx, gw, gb, None, None, None
 
 

@@ -44,7 +44,9 @@ def build_cases():
     # ---- mm: tails around the tile sizes, all four transposes --------------------------------
     shapes = [(1, 1, 1), (7, 5, 3), (33, 65, 17), (64, 64, 16), (65, 63, 15), (128, 128, 32),
               (129, 127, 33), (200, 72, 130), (256, 10, 128), (10, 128, 256), (300, 260, 47),
-              (4, 4, 0)]
+              (4, 4, 0),
+              # few outputs over a long K: the thin-tile configuration with several slabs in flight
+              (40, 70, 1100), (33, 31, 2049)]
     for si, (M, N, K) in enumerate(shapes):
         for ta in (False, True):
             for tb in (False, True):
