@@ -104,9 +104,12 @@ class _Conv2d(torch.autograd.Function):
             raise NotImplementedError("grouped convolution has no backward (as in the reference)")
         x, weight = ctx.saved_tensors
         need = ctx.needs_input_grad
-        gw, gb, gx = _concurrently(
-            (lambda: ops.conv2d_grad_kernel(x, weight.shape, g, stride, padding)) if need[1] else None,
+        # launch order matters: the two latency-bound operators first (measured on B200 for the second
+        # layer of the CNN workload: 0.95 ms in this order, 1.22 ms with the weight gradient first, 1.34 ms
+        # with the throughput-bound input gradient first, 1.38 ms one after the other)
+        gb, gw, gx = _concurrently(
             (lambda: ops.sum4d_dim023(g)) if need[2] else None,
+            (lambda: ops.conv2d_grad_kernel(x, weight.shape, g, stride, padding)) if need[1] else None,
             (lambda: ops.conv2d_grad_input(x.shape, weight, g, stride, padding)) if need[0] else None)
         return gx, gw, gb, None, None, None
 
