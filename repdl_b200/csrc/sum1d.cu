@@ -37,6 +37,8 @@
 // chain cannot hold -0).
 #include "common.cuh"
 
+#include <cooperative_groups.h>
+
 namespace repdl_b200 {
 namespace {
 
@@ -537,73 +539,80 @@ summarise_kernel(const float *__restrict__ x, int64_t n, const int2 *__restrict_
 // ---------------------------------------------------------------------------------------------
 // 4. the walk: one CTA; warp 0 walks, all warps prepare an opened node
 // ---------------------------------------------------------------------------------------------
-constexpr int WALK_THREADS = 512;   // 16 warps: each prepares two tiles of an opened node
+constexpr int WALK_THREADS = 512;   // 16 warps per CTA
+constexpr int WALK_CLUSTER = 4;     // CTAs (SMs) that prepare an opened node together
+constexpr int TPC = 32 / WALK_CLUSTER;  // tiles of a node per CTA: one (tile, binade) job per warp
+static_assert(TPC * 2 == WALK_THREADS / 32, "one job per warp");
 constexpr int RUN_PITCH = 36;  // floats per lane-run in shared memory: LDS.128 without bank conflicts
 struct WalkShared {
-    float raw[32][32 * RUN_PITCH];  // the 32 tiles of the opened node
-    Summ tile[2][32];               // tile summaries under the two binades of `e`
-    int leaf_lo[2][32][32], leaf_hi[2][32][32], leaf_c[2][32][32];  // leaf contexts, [binade][tile][lane]
-    int leaf_tot[2][32];
-    unsigned leaf_inv[2][32];
-    int e[2];
-    int cmd;                        // node to open, or -1: finished
+    float raw[TPC][32 * RUN_PITCH];  // this CTA's tiles of the opened node
+    Summ tile[2][TPC];               // their summaries under the two binades of `e`
+    int leaf_lo[2][TPC][32], leaf_hi[2][TPC][32], leaf_c[2][TPC][32];  // leaf contexts, [binade][tile][lane]
+    int leaf_tot[2][TPC];
+    unsigned leaf_inv[2][TPC];
+    int e[2];                        // (CTA 0 only) binades to summarise under
+    int cmd;                         // (CTA 0 only) node to open, or -1: finished
 };
 constexpr int WALK_SMEM_BYTES = (int)sizeof(WalkShared);
 
-__device__ __forceinline__ void cta_bar(int id)
-{
-    asm volatile("bar.sync %0, %1;" ::"r"(id), "n"(WALK_THREADS) : "memory");
-}
-
-// All warps: stage the 32 tiles of node nd in shared memory and summarise them under sh.e[0..1].
-__device__ __forceinline__ void prepare_node(WalkShared &sh, const float *__restrict__ x, int64_t n,
-                                             int nd, bool vec)
+// Every warp of every CTA of the cluster: one tile of node nd under one of the two binades that the
+// walker left in CTA 0's shared memory (`ctl`).  Tile tl of the node lives in CTA tl / TPC.
+__device__ __forceinline__ void prepare_node(WalkShared &sh, const WalkShared *ctl, int rank,
+                                             const float *__restrict__ x, int64_t n, int nd, bool vec)
 {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int tl = warp; tl < 32; tl += WALK_THREADS / 32) {
-        float v[LEAF];
-        load_leaf(x, n, (int64_t)nd * NODE + (int64_t)tl * TILE, vec, v);
+    const int tl = warp >> 1, h = warp & 1;
+    const int E = ctl->e[h];
+    float v[LEAF];
+    load_leaf(x, n, (int64_t)nd * NODE + (int64_t)(rank * TPC + tl) * TILE, vec, v);
+    if (h == 0) {
         float4 *dst = reinterpret_cast<float4 *>(&sh.raw[tl][lane * RUN_PITCH]);
 #pragma unroll
         for (int i = 0; i < LEAF / 4; i++)
             dst[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-#pragma unroll
-        for (int h = 0; h < 2; h++) {
-            bool tie;
-            const Summ leaf = leaf_summary(v, sh.e[h], &tie);
-            LeafCtx cx;
-            leaf_ctx_from_summary(cx, leaf, tie, sh.e[h]);
-            sh.leaf_lo[h][tl][lane] = cx.lo;
-            sh.leaf_hi[h][tl][lane] = cx.hi;
-            sh.leaf_c[h][tl][lane] = cx.c;
-            const Summ t = warp_reduce_summ(leaf);
-            if (lane == 0) {
-                sh.tile[h][tl] = t;
-                sh.leaf_tot[h][tl] = cx.tot;
-                sh.leaf_inv[h][tl] = cx.invmask;
-            }
-        }
+    }
+    bool tie;
+    const Summ leaf = leaf_summary(v, E, &tie);
+    LeafCtx cx;
+    leaf_ctx_from_summary(cx, leaf, tie, E);
+    sh.leaf_lo[h][tl][lane] = cx.lo;
+    sh.leaf_hi[h][tl][lane] = cx.hi;
+    sh.leaf_c[h][tl][lane] = cx.c;
+    const Summ t = warp_reduce_summ(leaf);
+    if (lane == 0) {
+        sh.tile[h][tl] = t;
+        sh.leaf_tot[h][tl] = cx.tot;
+        sh.leaf_inv[h][tl] = cx.invmask;
     }
 }
 
+// Launched as ONE cluster of WALK_CLUSTER CTAs.  Warp 0 of CTA 0 carries the exact state; everything
+// else only helps to prepare opened nodes.  The CTAs meet at the cluster's hardware barrier (no
+// spinning on memory): A -- a command is posted; B -- the node is prepared.  Between B and the next A
+// the walker reads the other CTAs' shared memory (distributed shared memory), which nobody writes then.
 __global__ void __launch_bounds__(WALK_THREADS, 1)
 walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__restrict__ hyp,
             const int4 *__restrict__ nodeA, const int4 *__restrict__ nodeB, float factor,
             float *__restrict__ out, int vec, int *__restrict__ stats)
 {
+    namespace cg = cooperative_groups;
     extern __shared__ __align__(16) unsigned char walk_smem[];
     WalkShared &sh = *reinterpret_cast<WalkShared *>(walk_smem);
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank();
+    const WalkShared *ctl = cluster.map_shared_rank(&sh, 0);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
-    if (warp != 0) {
+    if (rank != 0 || warp != 0) {
         // helpers: wait for a node to prepare until the walker says it is done
         while (true) {
-            cta_bar(1);
-            const int nd = sh.cmd;
+            cluster.sync();  // A
+            const int nd = ctl->cmd;
             if (nd < 0) break;
-            prepare_node(sh, x, n, nd, vec != 0);
-            cta_bar(2);
+            prepare_node(sh, ctl, rank, x, n, nd, vec != 0);
+            cluster.sync();  // B
         }
+        cluster.sync();  // nobody leaves while CTA 0's shared memory may still be read
         return;
     }
 
@@ -634,7 +643,7 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
             s, count, gE0, gE1, [&](int k) { return node_summ(k ? gE1 : gE0); },
             [&](int E) { return node_summ(E); },
             [&](int j, float sj) {
-                // open node g0 + j: every warp prepares tiles of it under the exact binade of the
+                // open node g0 + j: the cluster prepares its tiles under the exact binade of the
                 // state and the neighbouring binade the state is closer to
                 if (lane == 0) {
                     const int E = exp_field(sj);
@@ -643,32 +652,35 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
                     sh.cmd = g0 + j;
                 }
                 const long long tp = clock64();
-                cta_bar(1);
-                prepare_node(sh, x, n, g0 + j, vec != 0);
-                cta_bar(2);
+                cluster.sync();  // A
+                prepare_node(sh, ctl, 0, x, n, g0 + j, vec != 0);
+                cluster.sync();  // B
                 clk.prepare += clock64() - tp;
                 const int e0 = sh.e[0], e1 = sh.e[1];
-                const Summ ta = sh.tile[0][lane], tb = sh.tile[1][lane];
+                const WalkShared *mine = cluster.map_shared_rank(&sh, lane / TPC);  // holds tile `lane`
+                const Summ ta = mine->tile[0][lane % TPC], tb = mine->tile[1][lane % TPC];
                 return walk_level(
                     sj, 32, e0, e1, [&](int k) { return k ? tb : ta; },
                     [&](int) { return summ_invalid(); },
                     [&](int jt, float st) {
                         // open tile jt: its 32 leaves, summarised under the same two binades
                         const long long tl0 = clock64();
+                        const WalkShared *own = cluster.map_shared_rank(&sh, jt / TPC);
+                        const int jl = jt % TPC;
                         float v[LEAF];
-                        const float4 *src = reinterpret_cast<const float4 *>(&sh.raw[jt][lane * RUN_PITCH]);
+                        const float4 *src = reinterpret_cast<const float4 *>(&own->raw[jl][lane * RUN_PITCH]);
 #pragma unroll
                         for (int i = 0; i < LEAF / 4; i++) {
                             float4 t = src[i];
                             v[4 * i] = t.x, v[4 * i + 1] = t.y, v[4 * i + 2] = t.z, v[4 * i + 3] = t.w;
                         }
                         LeafCtx ca, cb;
-                        ca.lo = sh.leaf_lo[0][jt][lane], ca.hi = sh.leaf_hi[0][jt][lane];
-                        ca.c = sh.leaf_c[0][jt][lane], ca.tot = sh.leaf_tot[0][jt];
-                        ca.invmask = sh.leaf_inv[0][jt], ca.E = e0, ca.pos0 = 0;
-                        cb.lo = sh.leaf_lo[1][jt][lane], cb.hi = sh.leaf_hi[1][jt][lane];
-                        cb.c = sh.leaf_c[1][jt][lane], cb.tot = sh.leaf_tot[1][jt];
-                        cb.invmask = sh.leaf_inv[1][jt], cb.E = e1, cb.pos0 = 0;
+                        ca.lo = own->leaf_lo[0][jl][lane], ca.hi = own->leaf_hi[0][jl][lane];
+                        ca.c = own->leaf_c[0][jl][lane], ca.tot = own->leaf_tot[0][jl];
+                        ca.invmask = own->leaf_inv[0][jl], ca.E = e0, ca.pos0 = 0;
+                        cb.lo = own->leaf_lo[1][jl][lane], cb.hi = own->leaf_hi[1][jl][lane];
+                        cb.c = own->leaf_c[1][jl][lane], cb.tot = own->leaf_tot[1][jl];
+                        cb.invmask = own->leaf_inv[1][jl], cb.E = e1, cb.pos0 = 0;
                         clk.load += clock64() - tl0;
                         return walk_leaves(st, v, ca, cb, leaf_opens, clk);
                     },
@@ -685,7 +697,8 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
         cl[0] = clock64() - t_begin, cl[1] = clk.prepare, cl[2] = clk.leaf_steps, cl[3] = clk.raw;
         cl[4] = clk.rebuild, cl[5] = clk.load;
     }
-    cta_bar(1);  // releases the helpers
+    cluster.sync();  // A: releases the helpers
+    cluster.sync();  // everybody has read the command
 }
 
 // Short chains: one thread walks shared-memory tiles that the rest of the CTA stages.
@@ -789,8 +802,25 @@ static int sum1d_long(const float *x, float *out, int64_t n, float factor, char 
     if ((e = launch_status())) return e;
     static unsigned long long smem_done = 0;
     if ((e = ensure_smem(walk_kernel, WALK_SMEM_BYTES, &smem_done))) return e;
-    walk_kernel<<<1, WALK_THREADS, WALK_SMEM_BYTES, st>>>(x, n, (int)nn, hyp, nodeA, nodeB, factor, out,
-                                                          vec, reinterpret_cast<int *>(base + L.off_stats));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(WALK_CLUSTER);
+    cfg.blockDim = dim3(WALK_THREADS);
+    cfg.dynamicSmemBytes = WALK_SMEM_BYTES;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = WALK_CLUSTER;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    cudaError_t le = cudaLaunchKernelEx(&cfg, walk_kernel, x, n, (int)nn, (const int2 *)hyp,
+                                        (const int4 *)nodeA, (const int4 *)nodeB, factor, out, vec,
+                                        reinterpret_cast<int *>(base + L.off_stats));
+    if (le != cudaSuccess) {
+        (void)cudaGetLastError();
+        return (int)le;
+    }
     return launch_status();
 }
 
