@@ -240,8 +240,8 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
             want = gold["c3_sum1d_2p30"]["state_after_chunk_hex"][flat.numel() // (1 << 24) - 1]
             rec["bits_equal_reference_cpu"] = (
                 "%08x" % (y.cpu().view(torch.int32).item() & 0xFFFFFFFF)) == want
-        # how the walk went: opened nodes / tiles / leaves and the walker's cycle counters, which the
-        # kernel leaves in the first bytes of its scratch buffer
+        # how the walk went: opened nodes / tiles / leaves (and, in a build with clocks, the walker's
+        # cycle counters), which the kernel leaves in the first bytes of its scratch buffer
         from repdl_b200._cabi import check, lib
         nb = lib.repdl_b200_sum1d_scratch_bytes(flat.numel())
         if nb >= 80:
@@ -253,9 +253,11 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
             opens = sc[:16].view(torch.int32).tolist()
             cyc = sc[16:64].view(torch.int64).tolist()
             rec["walk"] = {"nodes": opens[3], "opened_nodes": opens[0], "opened_tiles": opens[1],
-                           "opened_leaves": opens[2], "cycles_total": cyc[0], "cycles_prepare_nodes": cyc[1],
-                           "cycles_leaf_level": cyc[2], "cycles_leaf_adds": cyc[3],
-                           "cycles_leaf_rebuild": cyc[4]}
+                           "opened_leaves": opens[2]}
+            if cyc[0]:  # only a library built with -DREPDL_SUM1D_CLOCKS=1 counts cycles
+                rec["walk"].update({"cycles_total": cyc[0], "cycles_prepare_nodes": cyc[1],
+                                    "cycles_leaf_level": cyc[2], "cycles_leaf_adds": cyc[3],
+                                    "cycles_leaf_rebuild": cyc[4]})
         out["sum1d chain [%d]" % flat.numel()] = rec
     return out
 

@@ -73,18 +73,6 @@ __device__ __forceinline__ Summ summ_compose(const Summ &a, const Summ &b)
     return r;
 }
 
-__device__ __forceinline__ Summ summ_negate(const Summ &s)
-{
-    if (summ_is_invalid(s)) return s;
-    return {-s.d0, -s.d1, s.hi <= -BIGI / 2 ? BIGI : -s.hi, s.lo >= BIGI / 2 ? -BIGI : -s.lo};
-}
-
-__device__ __forceinline__ Summ shfl_summ(const Summ &s, int src)
-{
-    return {__shfl_sync(0xffffffffu, s.d0, src), __shfl_sync(0xffffffffu, s.d1, src),
-            __shfl_sync(0xffffffffu, s.lo, src), __shfl_sync(0xffffffffu, s.hi, src)};
-}
-
 __device__ __forceinline__ Summ shfl_up_summ(const Summ &s, int delta)
 {
     return {__shfl_up_sync(0xffffffffu, s.d0, delta), __shfl_up_sync(0xffffffffu, s.d1, delta),
@@ -268,6 +256,20 @@ __device__ __forceinline__ float walk_level(float s, int count, int hypE0, int h
 // and only leaves of opened tiles pass through here, so this costs a handful of extra leaf walks.
 // ------------------------------------------------------------------------------------------------
 // Cycle counters of the walker warp, kept in the scratch header for diagnostics.
+// Cycle counters of the walker (diagnostics in the scratch header); compiled out unless asked for,
+// since reading the clock a few times per opened leaf is itself a measurable part of the walk.
+#ifndef REPDL_SUM1D_CLOCKS
+#define REPDL_SUM1D_CLOCKS 0
+#endif
+__device__ __forceinline__ long long walk_clock()
+{
+#if REPDL_SUM1D_CLOCKS
+    return clock64();
+#else
+    return 0;
+#endif
+}
+
 struct WalkClock {
     long long prepare, tile_scan, leaf_steps, raw, rebuild, load;
 };
@@ -340,7 +342,7 @@ __device__ __forceinline__ float walk_leaves(float s, const float (&v)[LEAF], Le
                                              int &opens, WalkClock &clk)
 {
     const int lane = threadIdx.x & 31;
-    const long long t_enter = clock64();
+    const long long t_enter = walk_clock();
     int pos = 0;
     bool done = false;
     auto step = [&](LeafCtx &c) {
@@ -367,31 +369,53 @@ __device__ __forceinline__ float walk_leaves(float s, const float (&v)[LEAF], Le
         const int j = __ffs((int)badmask) - 1;
         if (j > pos) s = apply_inc(s, __shfl_sync(0xffffffffu, m_in, j) - m);
         // open leaf j: 32 real fp32 adds by its owner
-        const long long t0 = clock64();
+        const long long t0 = walk_clock();
         float r = s;
         if (lane == j) {
 #pragma unroll
             for (int i = 0; i < LEAF; i++) r = __fadd_rn(r, v[i]);
         }
         s = __shfl_sync(0xffffffffu, r, j);
-        clk.raw += clock64() - t0;
+        clk.raw += walk_clock() - t0;
         opens++;
         pos = j + 1;
     };
+#ifndef REPDL_SUM1D_RAW3
+#define REPDL_SUM1D_RAW3 3
+#endif
+    int raw_run = 0;  // leaves walked with real adds in a row because the state sat in a third binade
     while (pos < 32 && !done) {
         const int E = exp_field(s);
         if (E == cxA.E) {
             step(cxA);
-        } else {
-            if (E != cxB.E) {
-                const long long t0 = clock64();
-                leaf_ctx_build(cxB, v, E, pos);
-                clk.rebuild += clock64() - t0;
-            }
+            raw_run = 0;
+        } else if (E == cxB.E) {
             step(cxB);
+            raw_run = 0;
+        } else if (raw_run < REPDL_SUM1D_RAW3) {
+            // A third binade (the state is crossing several binades, typically near zero): the next
+            // leaf's 32 real adds cost a fraction of a new context, and the state has often moved on
+            // to a prepared binade after them.
+            const long long t0 = walk_clock();
+            float r = s;
+            if (lane == pos) {
+#pragma unroll
+                for (int i = 0; i < LEAF; i++) r = __fadd_rn(r, v[i]);
+            }
+            s = __shfl_sync(0xffffffffu, r, pos);
+            clk.raw += walk_clock() - t0;
+            opens++;
+            pos++;
+            raw_run++;
+        } else {
+            const long long t0 = walk_clock();
+            leaf_ctx_build(cxB, v, E, pos);
+            clk.rebuild += walk_clock() - t0;
+            step(cxB);
+            raw_run = 0;
         }
     }
-    clk.leaf_steps += clock64() - t_enter;
+    clk.leaf_steps += walk_clock() - t_enter;
     return s;
 }
 
@@ -619,7 +643,7 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
     float s = 0.0f;
     int node_opens = 0, tile_opens = 0, leaf_opens = 0;
     WalkClock clk = {0, 0, 0, 0, 0, 0};
-    const long long t_begin = clock64();
+    const long long t_begin = walk_clock();
     for (int g0 = 0; g0 < nnodes; g0 += 32) {
         const int count = min(32, nnodes - g0);
         const int node = g0 + lane;
@@ -651,11 +675,11 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
                     sh.e[1] = (__float_as_int(sj) & 0x400000) ? E + 1 : E - 1;
                     sh.cmd = g0 + j;
                 }
-                const long long tp = clock64();
+                const long long tp = walk_clock();
                 cluster.sync();  // A
                 prepare_node(sh, ctl, 0, x, n, g0 + j, vec != 0);
                 cluster.sync();  // B
-                clk.prepare += clock64() - tp;
+                clk.prepare += walk_clock() - tp;
                 const int e0 = sh.e[0], e1 = sh.e[1];
                 const WalkShared *mine = cluster.map_shared_rank(&sh, lane / TPC);  // holds tile `lane`
                 const Summ ta = mine->tile[0][lane % TPC], tb = mine->tile[1][lane % TPC];
@@ -664,7 +688,7 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
                     [&](int) { return summ_invalid(); },
                     [&](int jt, float st) {
                         // open tile jt: its 32 leaves, summarised under the same two binades
-                        const long long tl0 = clock64();
+                        const long long tl0 = walk_clock();
                         const WalkShared *own = cluster.map_shared_rank(&sh, jt / TPC);
                         const int jl = jt % TPC;
                         float v[LEAF];
@@ -681,7 +705,7 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
                         cb.lo = own->leaf_lo[1][jl][lane], cb.hi = own->leaf_hi[1][jl][lane];
                         cb.c = own->leaf_c[1][jl][lane], cb.tot = own->leaf_tot[1][jl];
                         cb.invmask = own->leaf_inv[1][jl], cb.E = e1, cb.pos0 = 0;
-                        clk.load += clock64() - tl0;
+                        clk.load += walk_clock() - tl0;
                         return walk_leaves(st, v, ca, cb, leaf_opens, clk);
                     },
                     tile_opens);
@@ -694,7 +718,7 @@ walk_kernel(const float *__restrict__ x, int64_t n, int nnodes, const int2 *__re
         // how many nodes / tiles / leaves had to be opened (diagnostics, first 16 bytes of scratch)
         stats[0] = node_opens, stats[1] = tile_opens, stats[2] = leaf_opens, stats[3] = nnodes;
         long long *cl = reinterpret_cast<long long *>(stats + 4);
-        cl[0] = clock64() - t_begin, cl[1] = clk.prepare, cl[2] = clk.leaf_steps, cl[3] = clk.raw;
+        cl[0] = walk_clock() - t_begin, cl[1] = clk.prepare, cl[2] = clk.leaf_steps, cl[3] = clk.raw;
         cl[4] = clk.rebuild, cl[5] = clk.load;
     }
     cluster.sync();  // A: releases the helpers
