@@ -433,7 +433,9 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         e2e_ms = float(t[0]) / ke
         e2e = {"value": flops_step / e2e_ms / 1e6, "unit": "GFLOP/s", "ms_per_step": e2e_ms,
-               "h2d_bytes_per_step": world * (a_host.numel() + b_host.numel()) * 4,
+               # several GPUs: every rank uploads its A panel and 1/world of B (the rest is gathered)
+               "h2d_bytes_per_step": (world * a_host.numel() + b_host.numel()) * 4 if world > 1
+               else (a_host.numel() + b_host.numel()) * 4,
                "d2h_bytes_per_step": world * c_host.numel() * 4}
 
     # parity of the timed result against the golden hash of the reference CPU backend

@@ -106,11 +106,73 @@ class ShardedMM:
         return self.C
 
 
-def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel):
+_copy_streams = {}
+
+
+def _side_streams(device):
+    key = torch.device(device).index
+    if key not in _copy_streams:
+        _copy_streams[key] = (torch.cuda.Stream(device=device), torch.cuda.Stream(device=device))
+    return _copy_streams[key]
+
+
+def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chunks=8):
     """End-to-end step with HOST operands: pinned A panel and B go to the device, the sharded
-    product runs, and this rank's panel of C comes back to pinned host memory."""
-    a_dev.copy_(a_host_panel, non_blocking=True)
-    b_dev.copy_(b_host, non_blocking=True)
-    C = sharded(a_dev, b_dev)
-    c_host_panel.copy_(sharded.my_rows(), non_blocking=True)
+    product runs, and this rank's panel of C comes back to pinned host memory.
+
+    One GPU: the step is a pipeline over `chunks` row blocks of A.  B and the blocks of A are uploaded
+    in that order on a copy stream, block i is multiplied as soon as it has arrived, and its rows of C
+    go back on a second copy stream while block i + 1 is multiplied, so after B only the first upload
+    and the last download are exposed.  (Rows of C are independent chains, so the bits are those of
+    the one-launch product.)
+
+    Several GPUs: every rank has the same B in host memory, so each uploads only its 1/world of B's
+    rows and the ranks all-gather B over NVLink -- world times less PCIe traffic for B than uploading
+    it everywhere -- before the sharded product; the C panel comes back at the end.
+    """
+    dev = a_dev.device
+    if sharded.world > 1:
+        kp = b_dev.shape[0] // sharded.world
+        if b_dev.shape[0] % sharded.world == 0 and b_dev.is_contiguous():
+            lo = sharded.rank * kp
+            a_dev.copy_(a_host_panel, non_blocking=True)
+            b_dev[lo:lo + kp].copy_(b_host[lo:lo + kp], non_blocking=True)
+            dist.all_gather_into_tensor(b_dev, b_dev[lo:lo + kp], group=sharded.group)
+        else:
+            a_dev.copy_(a_host_panel, non_blocking=True)
+            b_dev.copy_(b_host, non_blocking=True)
+        C = sharded(a_dev, b_dev)
+        c_host_panel.copy_(sharded.my_rows(), non_blocking=True)
+        return C
+    rows = a_dev.shape[0]
+    if dev.type != "cuda" or chunks <= 1 or rows % chunks or rows // chunks < 256:
+        a_dev.copy_(a_host_panel, non_blocking=True)
+        b_dev.copy_(b_host, non_blocking=True)
+        C = sharded(a_dev, b_dev)
+        c_host_panel.copy_(sharded.my_rows(), non_blocking=True)
+        return C
+    cur = torch.cuda.current_stream(dev)
+    up, down = _side_streams(dev)
+    step = rows // chunks
+    up.wait_stream(cur)      # the buffers may still be in use by what the caller queued before
+    down.wait_stream(cur)
+    arrived = []
+    with torch.cuda.stream(up):
+        b_dev.copy_(b_host, non_blocking=True)
+        for i in range(chunks):
+            a_dev[i * step:(i + 1) * step].copy_(a_host_panel[i * step:(i + 1) * step], non_blocking=True)
+            ev = torch.cuda.Event()
+            ev.record(up)
+            arrived.append(ev)
+    C = sharded.C
+    for i in range(chunks):
+        cur.wait_event(arrived[i])
+        sharded.mm_into(a_dev[i * step:(i + 1) * step], b_dev, C[i * step:(i + 1) * step])
+        sharded.kernel_launches += 1
+        done = torch.cuda.Event()
+        done.record(cur)
+        down.wait_event(done)
+        with torch.cuda.stream(down):
+            c_host_panel[i * step:(i + 1) * step].copy_(C[i * step:(i + 1) * step], non_blocking=True)
+    cur.wait_stream(down)    # the caller's stream order covers the whole step
     return C

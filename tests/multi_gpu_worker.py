@@ -37,6 +37,17 @@ def main():
         out[mode + "_mode"] = sh.mode
         if hasattr(sh, "p2p_error"):
             out["p2p_error"] = sh.p2p_error
+    # the host-operand step: A panel and 1/world of B uploaded, B gathered over NVLink, C panel back
+    from repdl_b200.dist import mm_from_host
+    a_host = a[sh.row0:sh.row0 + sh.Mp].cpu().pin_memory()
+    b_host = b.cpu().pin_memory()
+    a_dev, b_dev = torch.zeros_like(a_host, device=dev), torch.zeros_like(b_host, device=dev)
+    c_host = torch.zeros(sh.Mp, N).pin_memory()
+    dist.barrier()
+    c = mm_from_host(sh, a_host, b_host, a_dev, b_dev, c_host)
+    torch.cuda.synchronize()
+    out["from_host"] = bool(torch.equal(c, alone)) and bool(
+        torch.equal(c_host, alone[sh.row0:sh.row0 + sh.Mp].cpu())) and bool(torch.equal(b_dev, b))
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
     if rank == 0:

@@ -39,6 +39,21 @@ def _worker(rank, world, port, q):
             ok = False
         except ValueError:
             pass
+        # host-operand step: every rank uploads 1/world of B's rows and the ranks gather the rest
+        # (K = 34 divides by the world size; K = 33 above takes the upload-everything path)
+        from repdl_b200.dist import mm_from_host
+        for K2 in (34, 33):
+            a2 = torch.rand(M, K2, generator=g) * 2 - 1
+            b2 = torch.rand(K2, N, generator=g) * 2 - 1
+            sh2 = ShardedMM(M, N, K2, device="cpu", mode="nccl", mm_into=mm_into)
+            a_dev, b_dev = torch.zeros(sh2.Mp, K2), torch.full((K2, N), float("nan"))
+            c_host = torch.zeros(sh2.Mp, N)
+            c2 = mm_from_host(sh2, a2[sh2.row0:sh2.row0 + sh2.Mp], b2, a_dev, b_dev, c_host)
+            full2 = oracle.mm(a2, b2)
+            ok = ok and torch.equal(c2.view(torch.int32), full2.view(torch.int32))
+            ok = ok and torch.equal(c_host.view(torch.int32),
+                                    full2[sh2.row0:sh2.row0 + sh2.Mp].view(torch.int32))
+            ok = ok and torch.equal(b_dev.view(torch.int32), b2.view(torch.int32))
         q.put((rank, ok, sh.kernel_launches))
     finally:
         dist.destroy_process_group()

@@ -28,5 +28,5 @@ def test_row_sharded_mm_matches_single_gpu():
     ranks = json.loads(line[len("RESULT "):])
     assert len(ranks) == world
     for r in ranks:
-        for key in ("nccl_0", "nccl_1", "auto_0", "auto_1"):
+        for key in ("nccl_0", "nccl_1", "auto_0", "auto_1", "from_host"):
             assert r[key], (r, key)

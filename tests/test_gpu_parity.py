@@ -137,6 +137,30 @@ def test_mm_linearity_in_rows(ops):
         assert torch.equal(full[lo:hi], ops.mm(a[lo:hi], b))
 
 
+def test_mm_from_host_pipeline_equals_one_launch(ops):
+    """The pipelined host-operand step (row blocks uploaded, multiplied and downloaded on three
+    streams) gives the bits of the one-launch product, twice in a row on the same buffers."""
+    from repdl_b200.dist import ShardedMM, mm_from_host
+    M, N, K = 4096, 640, 300
+    g = torch.Generator().manual_seed(77)
+    a = (torch.rand(M, K, generator=g) * 2 - 1)
+    b = (torch.rand(K, N, generator=g) * 2 - 1)
+    want = ops.mm(a.cuda(), b.cuda())
+    sh = ShardedMM(M, N, K, device="cuda")
+    a_host, b_host = a.pin_memory(), b.pin_memory()
+    a_dev, b_dev = torch.zeros(M, K, device="cuda"), torch.zeros(K, N, device="cuda")
+    c_host = torch.zeros(M, N).pin_memory()
+    for rep in range(2):
+        sh.C.zero_()
+        c_host.zero_()
+        sh.kernel_launches = 0
+        c = mm_from_host(sh, a_host, b_host, a_dev, b_dev, c_host, chunks=8)
+        torch.cuda.synchronize()
+        assert sh.kernel_launches == 8
+        assert torch.equal(c.view(torch.int32), want.view(torch.int32))
+        assert torch.equal(c_host.view(torch.int32), want.cpu().view(torch.int32))
+
+
 def test_config3_full_chain_and_rows(ops):
     """Config 3 at full size: the 2^30-element chain (checked against the reference's running
     state after every quarter and at the end) and the [65536, 4096] row sums."""
