@@ -208,7 +208,9 @@ def build_cases():
                               lambda M=M, N=N, kd=kd, avg=avg: (_randn(710, M, N, scale=10.0), kd, avg)))
                 cases.append(("sum2d_dim1_%dx%d_%d%d" % (M, N, kd, avg), "sum2d_dim1",
                               lambda M=M, N=N, kd=kd, avg=avg: (_randn(711, M, N, scale=10.0), kd, avg)))
-    for (N, C, H, W) in [(3, 5, 7, 2), (4, 64, 24, 24), (2, 1, 1, 1), (5, 3, 13, 11)]:
+    # the last three: chains longer than one staged tile of 4096 with short, one-element and long segments
+    for (N, C, H, W) in [(3, 5, 7, 2), (4, 64, 24, 24), (2, 1, 1, 1), (5, 3, 13, 11), (40, 3, 11, 13),
+                         (5000, 2, 1, 1), (9, 2, 30, 31)]:
         for kd in (False, True):
             for avg in (False, True):
                 cases.append(("sum4d_%dx%dx%dx%d_%d%d" % (N, C, H, W, kd, avg), "sum4d_dim023",
