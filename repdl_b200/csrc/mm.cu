@@ -332,17 +332,30 @@ int launch_one(const float *A, const float *B, const OutSet &C, int M, int N, in
 #define REPDL_MM_TN 16
 #endif
 #define REPDL_MM_BIG REPDL_MM_BM, REPDL_MM_BN, REPDL_MM_TM, REPDL_MM_TN
+#ifndef REPDL_MM_ALT
+#define REPDL_MM_ALT 1   // 0: never use the 192 x 128 configuration
+#endif
 
 template <bool A_KC, bool B_KC, bool VEC>
 int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, int K, int64_t lda,
                  int64_t ldb, int64_t ldc, int vecC, cudaStream_t st)
 {
     // Big tiles once they fill the machine twice over; small tiles otherwise so that a
-    // 1024 x 1024 problem still spreads over all 148 SMs.
-    int64_t big = (int64_t)((M + REPDL_MM_BM - 1) / REPDL_MM_BM) * ((N + REPDL_MM_BN - 1) / REPDL_MM_BN);
-    if (big >= 2 * (int64_t)sm_count())
+    // 1024 x 1024 problem still spreads over all 148 SMs.  Two big configurations: 192 x 128 with
+    // 12 x 8 outputs per thread runs 3 % faster per FMA than 128 x 256 with 8 x 16 (its unrolled slab
+    // fits the instruction cache), but which one finishes first also depends on how the tile count
+    // rounds up to whole waves and how much of the edge tiles is padding, so both are costed.
+    const int64_t sms = sm_count();
+    const int64_t tiles_a = (int64_t)((M + 191) / 192) * ((N + 127) / 128);
+    const int64_t tiles_b = (int64_t)((M + REPDL_MM_BM - 1) / REPDL_MM_BM) * ((N + REPDL_MM_BN - 1) / REPDL_MM_BN);
+    if (tiles_a >= 2 * sms || tiles_b >= 2 * sms) {
+        const double cost_a = (double)((tiles_a + sms - 1) / sms) * (192.0 * 128.0) / 1.033;
+        const double cost_b = (double)((tiles_b + sms - 1) / sms) * ((double)REPDL_MM_BM * REPDL_MM_BN);
+        if (REPDL_MM_ALT && tiles_a >= 2 * sms && (cost_a < cost_b || tiles_b < 2 * sms))
+            return launch_one<192, 128, 12, 8, A_KC, B_KC, VEC, 1>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
         return launch_one<REPDL_MM_BIG, A_KC, B_KC, VEC, REPDL_MM_MINB_BIG>(A, B, C, M, N, K, lda,
                                                                            ldb, ldc, vecC, st);
+    }
     int64_t mid = (int64_t)((M + 127) / 128) * ((N + 63) / 64);
     if (mid >= 2 * (int64_t)sm_count())
         return launch_one<128, 64, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC,

@@ -46,7 +46,9 @@ def build_cases():
               (129, 127, 33), (200, 72, 130), (256, 10, 128), (10, 128, 256), (300, 260, 47),
               (4, 4, 0),
               # few outputs over a long K: the thin-tile configuration with several slabs in flight
-              (40, 70, 1100), (33, 31, 2049)]
+              (40, 70, 1100), (33, 31, 2049),
+              # ragged edges of the two large-tile configurations (192 x 128 and 128 x 256 outputs per CTA)
+              (2500, 3100, 37), (2040, 16380, 17)]
     for si, (M, N, K) in enumerate(shapes):
         for ta in (False, True):
             for tb in (False, True):
