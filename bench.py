@@ -462,11 +462,12 @@ def main():
                        "l2": "operands (3 GiB) exceed the 126 MB L2"},
             "roofline": {"bound": "fp32_ffma", "achieved": achieved, "peak": peak, "unit": "TFLOP/s",
                          "frac": achieved / peak,
-                         # DRAM bytes of one rank's launch: the ncu capture of the 16384^3 launch
-                         # (profiles/sgemm_mm16384_launch_list_and_dram.md: 35.58 GB), scaled by the
-                         # rows a rank computes (B is streamed once per group of 8 tile rows, so the
-                         # traffic is proportional to the rows); null for other sizes
-                         "traffic": (35.58e9 / world if n == 16384 else None),
+                         # DRAM bytes of one rank's launch: ncu captures of the 16384^3 launch (summarised
+                         # under profiles/), 27.53 GB with the 192 x 128 tile that 1 and 2 ranks get and
+                         # 35.58 GB with the 128 x 256 tile that 4 and 8 ranks get, scaled by the rows a
+                         # rank computes (B is streamed once per group of 8 tile rows, so the traffic is
+                         # proportional to the rows); null for other sizes
+                         "traffic": ((27.53e9 if world <= 2 else 35.58e9) / world if n == 16384 else None),
                          "algorithmic_bytes": 4.0 * (n * n / world + n * n + n * n / world),
                          "peak_source": "FFMA-only probe kernel timed in this run",
                          "peak_nominal": 148 * 128 * 2 * 1.965e9 / 1e12,
