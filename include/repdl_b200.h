@@ -146,6 +146,29 @@ int repdl_b200_softmax(const float *x, float *y, int64_t M, int64_t N, void *str
 int repdl_b200_cross_entropy(const float *x, const int64_t *target, float *loss, int64_t M,
                              int64_t N, float *row_scratch, void *stream);
 
+/* ---- optimizer steps ---------------------------------------------------------------------------
+ * One launch updates up to 24 parameter tensors (more: several launches).  params / grads / ... are
+ * HOST arrays of `ntensors` device pointers, sizes holds the element counts.  Every operation is
+ * rounded separately in fp32 in the order of the Python update it replaces.
+ *
+ * repdl_b200_adam_step replaces the per-tensor loop of Adam.step, microsoft/RepDL
+ * repdl/optim.py:56-83 (CUDA tensors reach ATen element-wise kernels and repdl.ops.sqrt / div there):
+ *   g' = fma(p, weight_decay, g) if weight_decay != 0;  m = fma(g', 1-beta1, m*beta1);
+ *   v = v*beta2 + (g'*g')*(1-beta2);  [vmax = maximum(vmax, v) if max_exp_avg_sq != NULL]
+ *   p += (m / (sqrt(v or vmax) / sqrt_bias_correction2 + eps)) * neg_step_size
+ * with the scalars already converted to fp32 the way ATen converts Python scalars
+ * (neg_step_size = -(lr / bias_correction1)).
+ *
+ * repdl_b200_sgd_step: p += g * neg_lr (two roundings, the style of repdl/optim.py:83; the reference
+ * itself ships no SGD). */
+int repdl_b200_sgd_step(float *const *params, const float *const *grads, const int64_t *sizes,
+                        int ntensors, float neg_lr, void *stream);
+int repdl_b200_adam_step(float *const *params, const float *const *grads, float *const *exp_avg,
+                         float *const *exp_avg_sq, float *const *max_exp_avg_sq,
+                         const int64_t *sizes, int ntensors, float beta1, float one_minus_beta1,
+                         float beta2, float one_minus_beta2, float sqrt_bias_correction2, float eps,
+                         float neg_step_size, float weight_decay, void *stream);
+
 /* ---- diagnostics (no counterpart in the reference) --------------------------------------------
  * Enqueues a kernel of nothing but independent FMAs on every SM (fp64 == 0: scalar fp32 FFMA,
  * 1: fp64 DFMA, 2: packed fp32 fma.rn.f32x2 -- two FMAs per instruction):

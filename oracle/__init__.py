@@ -225,3 +225,27 @@ def ref():
                 spec.loader.exec_module(rm)
                 _ref = _Ref(cpu, rm, site)
     return _ref
+
+
+def _f(v):
+    """A Python scalar the way ATen hands it to an fp32 kernel."""
+    return ctypes.c_float(float(torch.tensor(float(v), dtype=torch.float32)))
+
+
+def sgd_step(p, g, lr):
+    """In place on the fp32 CPU tensor p: p += g * -lr (two roundings)."""
+    assert p.dtype == torch.float32 and p.is_contiguous() and g.is_contiguous()
+    lib().oracle_sgd_step(_p(p), _p(_f32(g)), _i(p.numel()), _f(-lr))
+
+
+def adam_step(p, g, m, v, step, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0, vmax=None):
+    """One Adam.step of repdl/optim.py:56-83 for one parameter tensor, in place on p, m, v (and vmax
+    with amsgrad); `step` is the 1-based step count."""
+    import math
+    for t in (p, g, m, v) + ((vmax,) if vmax is not None else ()):
+        assert t.dtype == torch.float32 and t.is_contiguous()
+    b1, b2 = betas
+    bc1, bc2 = 1 - b1 ** step, 1 - b2 ** step
+    lib().oracle_adam_step(_p(p), _p(g), _p(m), _p(v), _p(vmax) if vmax is not None else None,
+                           _i(p.numel()), _f(b1), _f(1 - b1), _f(b2), _f(1 - b2), _f(math.sqrt(bc2)),
+                           _f(eps), _f(-(lr / bc1)), _f(weight_decay))

@@ -392,3 +392,47 @@ float oracle_cross_entropy(const float *x, const i64 *target, i64 M, i64 N, floa
     if (!per_row) free(l);
     return r;
 }
+
+/* ---- optimizer steps -------------------------------------------------------------------------
+ * Adam.step, repdl/optim.py:56-83, element by element in the order of the tensor operations there:
+ *   :67-68 grad.add(param, alpha=wd)            -> ATen add with alpha: one fused multiply-add
+ *   :70    exp_avg.mul_(b1).add_(grad, alpha=1-b1) -> a multiply, then one fused multiply-add
+ *   :71    exp_avg_sq.mul_(b2).add_(mul(grad, grad).mul(1-b2)) -> four separately rounded ops
+ *   :73-76 maximum (amsgrad), :77-82 div(sqrt(.), sqrt(bc2)).add_(eps), :83-84 the update.
+ * Python scalars reach the fp32 kernels converted to fp32; the callers pass them converted.
+ * vmax may be NULL (no amsgrad). */
+void oracle_adam_step(float *p, const float *g, float *m, float *v, float *vmax, i64 n, float beta1,
+                      float one_minus_beta1, float beta2, float one_minus_beta2, float sqrt_bc2,
+                      float eps, float neg_step_size, float weight_decay)
+{
+    for (i64 i = 0; i < n; i++) {
+        float gi = g[i];
+        if (weight_decay != 0.0f) gi = fmaf(p[i], weight_decay, gi);
+        const float mi = fmaf(gi, one_minus_beta1, m[i] * beta1);
+        const float gg = gi * gi;
+        const float vi = v[i] * beta2 + gg * one_minus_beta2;
+        m[i] = mi;
+        v[i] = vi;
+        float root = vi;
+        if (vmax) {
+            const float old = vmax[i];
+            root = (old != old) ? old : ((vi != vi) ? vi : (old > vi ? old : vi));
+            vmax[i] = root;
+        }
+        float sq;
+        oracle_sqrt(&root, &sq, 1);
+        const float denom = sq / sqrt_bc2 + eps;
+        const float upd = (mi / denom) * neg_step_size;
+        p[i] = p[i] + upd;
+    }
+}
+
+/* p <- p + (g * -lr): two separately rounded operations (the update style of repdl/optim.py:83;
+ * the reference has no SGD of its own). */
+void oracle_sgd_step(float *p, const float *g, i64 n, float neg_lr)
+{
+    for (i64 i = 0; i < n; i++) {
+        const float t = g[i] * neg_lr;
+        p[i] = p[i] + t;
+    }
+}

@@ -14,6 +14,8 @@ _ptr, _size = ctypes.c_void_p, ctypes.c_size_t
 
 # name -> (restype, argtypes); mirrors include/repdl_b200.h declaration by declaration
 SIGNATURES = {
+    "repdl_b200_sgd_step": (_int, [_ptr, _ptr, _ptr, _int, _f32, _ptr]),
+    "repdl_b200_adam_step": (_int, [_ptr, _ptr, _ptr, _ptr, _ptr, _ptr, _int] + [_f32] * 8 + [_ptr]),
     "repdl_b200_version": (_int, []),
     "repdl_b200_sm_arch": (_int, []),
     "repdl_b200_strerror": (ctypes.c_char_p, [_int]),

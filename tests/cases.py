@@ -300,3 +300,60 @@ class RefAdapter:
 
     def cross_entropy(self, x, t):
         return self.cpu.cross_entropy(x, t)
+
+
+# ---- optimizer steps ----------------------------------------------------------------------------
+OPTIM_SHAPES = [(37,), (5, 7), (300,), (1,), (64, 33)]
+OPTIM_CONFIGS = [  # name, weight_decay, amsgrad
+    ("plain", 0.0, False), ("decay", 0.01, False), ("amsgrad", 0.0, True), ("both", 0.02, True)]
+OPTIM_STEPS = 6
+
+
+def optim_inputs():
+    """Initial parameters and the gradients of every step (magnitudes from 1e-6 to 100)."""
+    g = torch.Generator().manual_seed(9)
+    params = [torch.randn(*s, generator=g) for s in OPTIM_SHAPES]
+    grads = []
+    for _ in range(OPTIM_STEPS):
+        grads.append([torch.randn(*s, generator=g) * 10 ** float(torch.randint(-6, 3, (1,), generator=g))
+                      for s in OPTIM_SHAPES])
+    return params, grads
+
+
+def run_optimizer(make_optimizer, device="cpu"):
+    """Runs OPTIM_STEPS steps of the optimizer `make_optimizer(params)` returns; the hash of all
+    parameters after every step."""
+    params, grads = optim_inputs()
+    ps = [torch.nn.Parameter(p.clone().to(device)) for p in params]
+    opt = make_optimizer(ps)
+    hashes = []
+    for step_grads in grads:
+        for p, gr in zip(ps, step_grads):
+            p.grad = gr.clone().to(device)
+        opt.step()
+        hashes.append(sha(torch.cat([p.detach().cpu().reshape(-1) for p in ps])))
+    return hashes
+
+
+def run_oracle_adam(oracle, weight_decay, amsgrad, lr=0.01):
+    params, grads = optim_inputs()
+    ps = [p.clone() for p in params]
+    ms, vs = [torch.zeros_like(p) for p in ps], [torch.zeros_like(p) for p in ps]
+    vm = [torch.zeros_like(p) for p in ps] if amsgrad else [None] * len(ps)
+    hashes = []
+    for st, step_grads in enumerate(grads, 1):
+        for p, gr, m, v, vx in zip(ps, step_grads, ms, vs, vm):
+            oracle.adam_step(p, gr.contiguous(), m, v, st, lr=lr, weight_decay=weight_decay, vmax=vx)
+        hashes.append(sha(torch.cat([p.reshape(-1) for p in ps])))
+    return hashes
+
+
+def run_oracle_sgd(oracle, lr=0.01):
+    params, grads = optim_inputs()
+    ps = [p.clone() for p in params]
+    hashes = []
+    for step_grads in grads:
+        for p, gr in zip(ps, step_grads):
+            oracle.sgd_step(p, gr.contiguous(), lr)
+        hashes.append(sha(torch.cat([p.reshape(-1) for p in ps])))
+    return hashes

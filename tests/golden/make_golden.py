@@ -8,6 +8,7 @@ machines that do not have the reference.
     python tests/golden/make_golden.py configs    # tests/golden/configs.json       (~15 min)
     python tests/golden/make_golden.py cnn        # tests/golden/cnn_steps.json     (~10 min)
     python tests/golden/make_golden.py mm16k      # tests/golden/mm16k.json         (~10 min)
+    python tests/golden/make_golden.py optim      # tests/golden/optim_steps.json   (seconds)
 
 Every value is produced by the reference's own CPU backend (repdl.backend.cpu, plus the exp2d /
 log1d shim and repdl/ops.py's ATen div / sqrt), except the full 16384^3 product, whose hash comes
@@ -155,10 +156,34 @@ def mm16k(ref):
     dump("mm16k.json", out)
 
 
+def optim(ref):
+    """Parameter hashes after each of six steps of the reference's own Adam (repdl/optim.py) on CPU
+    tensors, for four settings; and of the two-rounding SGD update written with torch's CPU ops."""
+    import cases
+    sys.path.insert(0, oracle.ref_site())
+    import repdl
+    out = {"_meta": meta()}
+    for name, wd, ams in cases.OPTIM_CONFIGS:
+        out["adam_" + name] = cases.run_optimizer(
+            lambda ps: repdl.optim.Adam(ps, lr=0.01, weight_decay=wd, amsgrad=ams))
+
+    class TwoRoundingSGD(torch.optim.Optimizer):
+        def __init__(self, params, lr):
+            super().__init__(params, dict(lr=lr))
+
+        @torch.no_grad()
+        def step(self):
+            for group in self.param_groups:
+                for p in group["params"]:
+                    p.add_(p.grad.mul(-group["lr"]))
+    out["sgd"] = cases.run_optimizer(lambda ps: TwoRoundingSGD(ps, 0.01))
+    dump("optim_steps.json", out)
+
+
 if __name__ == "__main__":
     ref = oracle.ref()
     if ref is None:
         sys.exit("oracle/_ref is not built (run oracle/build_ref.sh where the reference is mounted)")
     what = sys.argv[1:] or ["small"]
     for w in what:
-        {"small": small, "configs": configs, "cnn": cnn, "mm16k": mm16k}[w](ref)
+        {"small": small, "configs": configs, "cnn": cnn, "mm16k": mm16k, "optim": optim}[w](ref)

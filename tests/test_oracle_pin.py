@@ -79,3 +79,28 @@ def test_config1_hash():
     from repdl_b200 import workloads
     a, b = workloads.mm_square(1024, 0)
     assert sha(oracle.mm(a, b)) == golden("configs.json")["c1_mm_1024"]["sha256"]
+
+
+# ---- optimizer steps: the oracle's restatement of Adam.step (repdl/optim.py:56-83) and the SGD update
+@pytest.mark.parametrize("name,wd,ams", [c for c in __import__("cases").OPTIM_CONFIGS],
+                         ids=[c[0] for c in __import__("cases").OPTIM_CONFIGS])
+def test_oracle_adam_matches_golden(name, wd, ams):
+    import cases
+    assert cases.run_oracle_adam(oracle, wd, ams) == golden("optim_steps.json")["adam_" + name]
+
+
+def test_oracle_sgd_matches_golden():
+    import cases
+    assert cases.run_oracle_sgd(oracle) == golden("optim_steps.json")["sgd"]
+
+
+@pytest.mark.skipif(oracle.ref_site() is None, reason="reference not built into oracle/_ref here")
+def test_oracle_adam_matches_reference_live():
+    import sys
+
+    import cases
+    sys.path.insert(0, oracle.ref_site())
+    import repdl
+    for name, wd, ams in cases.OPTIM_CONFIGS:
+        want = cases.run_optimizer(lambda ps: repdl.optim.Adam(ps, lr=0.01, weight_decay=wd, amsgrad=ams))
+        assert cases.run_oracle_adam(oracle, wd, ams) == want, name
