@@ -1,0 +1,89 @@
+"""GPU: seeded random shapes through the operators with many code paths (convolutions and their
+gradients: padding, strides, ragged tiles, row chunks of every length, rows wider than a chunk;
+products around every tile size; chain sums), each compared bit for bit with the CPU oracle.  The
+oracle itself is pinned to the reference on the fixed cases of tests/cases.py."""
+import random
+
+import pytest
+import torch
+
+import oracle
+
+pytestmark = pytest.mark.gpu
+
+
+def bits_equal(a, b):
+    a, b = a.detach().cpu().contiguous(), b.detach().cpu().contiguous()
+    return a.shape == b.shape and torch.equal(a.view(torch.int32).reshape(-1), b.view(torch.int32).reshape(-1))
+
+
+def _randn(g, *shape):
+    # a few exact zeros and a wide range of magnitudes, no non-finite values
+    x = torch.randn(*shape, generator=g)
+    scale = 10.0 ** torch.randint(-3, 3, (1,), generator=g).item()
+    x = x * scale
+    if x.numel() > 4:
+        x.view(-1)[:: max(3, x.numel() // 7)] = 0.0
+    return x
+
+
+def conv_configs(seed, count):
+    rnd = random.Random(seed)
+    out = []
+    while len(out) < count:
+        wide = rnd.random() < 0.1
+        N, IC, OC = rnd.randint(1, 6), rnd.randint(1, 9), rnd.randint(1, 20)
+        H, W = rnd.randint(3, 40), (rnd.randint(260, 600) if wide else rnd.randint(3, 40))
+        if wide:
+            H, N = rnd.randint(3, 6), rnd.randint(1, 2)
+        KH, KW = rnd.randint(1, 5), rnd.randint(1, 5)
+        sH, sW = rnd.randint(1, 3), rnd.randint(1, 3)
+        pH, pW = rnd.choice([0, 0, 1, 2, 3]), rnd.choice([0, 0, 1, 2, 3])
+        if H + 2 * pH < KH or W + 2 * pW < KW:
+            continue
+        out.append((N, IC, H, W, OC, KH, KW, (sH, sW), (pH, pW)))
+    return out
+
+
+@pytest.mark.parametrize("cfg", conv_configs(20240, 60), ids=lambda c: "x".join(map(str, c[:7])) + "_s%d%d_p%d%d" % (c[7] + c[8]))
+def test_conv_and_gradients_random_shapes(cfg):
+    from repdl_b200 import ops
+    N, IC, H, W, OC, KH, KW, s, p = cfg
+    g = torch.Generator().manual_seed(hash(cfg) & 0xFFFFFF)
+    OH, OW = (H + 2 * p[0] - KH) // s[0] + 1, (W + 2 * p[1] - KW) // s[1] + 1
+    x, k, go = _randn(g, N, IC, H, W), _randn(g, OC, IC, KH, KW), _randn(g, N, OC, OH, OW)
+    xd, kd, god = x.cuda(), k.cuda(), go.cuda()
+    assert bits_equal(ops.conv2d(xd, kd, s, p, 1), oracle.conv2d(x, k, s, p, 1))
+    assert bits_equal(ops.conv2d_grad_input(x.shape, kd, god, s, p), oracle.conv2d_grad_input(x.shape, k, go, s, p))
+    assert bits_equal(ops.conv2d_grad_kernel(xd, k.shape, god, s, p), oracle.conv2d_grad_kernel(x, k.shape, go, s, p))
+
+
+def mm_shapes(seed, count):
+    rnd = random.Random(seed)
+    return [(rnd.randint(1, 420), rnd.randint(1, 420), rnd.choice([0, 1, 15, 16, 17, rnd.randint(1, 700)]),
+             rnd.random() < 0.5, rnd.random() < 0.5) for _ in range(count)]
+
+
+@pytest.mark.parametrize("shape", mm_shapes(77, 40), ids=lambda s: "%dx%dx%d_%d%d" % s)
+def test_mm_random_shapes(shape):
+    from repdl_b200 import ops
+    M, N, K, ta, tb = shape
+    g = torch.Generator().manual_seed(M * 1000003 + N * 1009 + K)
+    a = _randn(g, *((K, M) if ta else (M, K)))
+    b = _randn(g, *((N, K) if tb else (K, N)))
+    assert bits_equal(ops.mm(a.cuda(), b.cuda(), ta, tb), oracle.mm(a, b, ta, tb))
+
+
+def test_chain_sums_random_shapes():
+    from repdl_b200 import ops
+    rnd = random.Random(5)
+    g = torch.Generator().manual_seed(5)
+    for _ in range(25):
+        N, C, H, W = rnd.randint(1, 70), rnd.randint(1, 9), rnd.randint(1, 33), rnd.randint(1, 33)
+        x = _randn(g, N, C, H, W)
+        for avg in (False, True):
+            assert bits_equal(ops.sum4d_dim023(x.cuda(), False, avg), oracle.sum4d_dim023(x, False, avg)), (N, C, H, W)
+        M, K = rnd.randint(1, 300), rnd.randint(1, 5000)
+        y = _randn(g, M, K)
+        assert bits_equal(ops.sum2d_dim0(y.cuda()), oracle.sum2d_dim0(y)), (M, K)
+        assert bits_equal(ops.sum2d_dim1(y.cuda()), oracle.sum2d_dim1(y)), (M, K)
