@@ -133,6 +133,33 @@ def load_reference_cpu():
     return "port", lambda a, b, ta, tb: oracle.mm(a, b, ta, tb), oracle.num_threads()
 
 
+def cpu_side(op, x, bytes_per_element):
+    """The reference's CPU path for one of the streaming operators, timed on the host cores on the
+    sample x (a CPU tensor): its own backend where oracle/_ref is built, else the C oracle port."""
+    import oracle
+    ref = oracle.ref()
+    if ref is not None:
+        kind, cores = "reference", torch.get_num_threads()
+        fns = {"div10": lambda t: t.div(10.0),                                      # repdl/ops.py:98-103
+               "sqrt": lambda t: t.to(torch.float64).sqrt().to(torch.float32),      # repdl/ops.py:122-123
+               "exp": lambda t: ref.math.exp2d(t.view(1, -1)),
+               "log": lambda t: ref.math.log1d(t),
+               "sum_rows": lambda t: ref.cpu.sum2d_dim1(t, False, False),
+               "sum1d": lambda t: ref.cpu.sum1d(t, False)}
+    else:
+        kind, cores = "port", oracle.num_threads()
+        fns = {"div10": lambda t: oracle.div(t, 10.0), "sqrt": oracle.sqrt, "exp": oracle.exp,
+               "log": oracle.log, "sum_rows": oracle.sum2d_dim1, "sum1d": oracle.sum1d}
+    fn = fns[op]
+    fn(x)
+    t0 = time.perf_counter()
+    fn(x)
+    dt = time.perf_counter() - t0
+    return {"value": bytes_per_element * x.numel() / dt / 1e9, "unit": "GB/s",
+            "cores": 1 if op == "sum1d" else cores, "kind": kind,
+            "sample": "%d elements (%.0f ms)" % (x.numel(), dt * 1e3)}
+
+
 def time_cpu_mm(a, b, budget_s, rows0=4):
     """Times the CPU mm on the first rows of A; grows the sample until it fills the budget."""
     kind, fn, cores = load_reference_cpu()
@@ -203,6 +230,9 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
         x = torch.cat(list(workloads.crmath_chunks(n, 1)))
         xa = x.abs()  # on the CPU: torch's CUDA abs() would canonicalise NaN payloads
         xd, xad = x.cuda(), xa.cuda()
+        cs = min(n, 1 << 24)  # CPU sample: the first 2^24 elements
+        cpu = {"div(x,10)": cpu_side("div10", x[:cs].clone(), 8), "sqrt(|x|)": cpu_side("sqrt", xa[:cs].clone(), 8),
+               "exp(x)": cpu_side("exp", x[:cs].clone(), 8), "log(|x|)": cpu_side("log", xa[:cs].clone(), 8)}
         del x, xa
         for name, fn, key in (("div(x,10)", lambda: ops.div(xd, 10.0), "div10"),
                               ("sqrt(|x|)", lambda: ops.sqrt(xad), "sqrt_abs"),
@@ -210,7 +240,8 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
                               ("log(|x|)", lambda: ops.log(xad), "log_abs")):
             ms, y = measure(fn)
             rec = {"ms": ms, "GB/s": 8.0 * n / ms / 1e6,
-                   "frac_of_%s_hbm" % peak_kind: 8.0 * n / ms / 1e6 / hbm_peak, "elements": n}
+                   "frac_of_%s_hbm" % peak_kind: 8.0 * n / ms / 1e6 / hbm_peak, "elements": n,
+                   "cpu_baseline": cpu[name]}
             if gold:
                 rec["sha256_equal_reference_cpu"] = (
                     hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
@@ -222,10 +253,16 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
     if which in ("all", "sums"):
         # rows x 4096 matrix from the first n elements of the config-3 stream
         rows = n // 4096
-        r = torch.cat(list(workloads.sum_chunks(rows * 4096, 2))).view(rows, 4096).cuda()
+        r_cpu = torch.cat(list(workloads.sum_chunks(rows * 4096, 2))).view(rows, 4096)
+        crows = min(rows, 4096)  # CPU sample: the first 2^24 elements
+        cpu_rows = cpu_side("sum_rows", r_cpu[:crows].clone(), 4)
+        cpu_chain = cpu_side("sum1d", r_cpu[:crows].clone().view(-1), 4)
+        r = r_cpu.cuda()
+        del r_cpu
         ms, y = measure(lambda: ops.sum2d_dim1(r))
         rec = {"ms": ms, "GB/s": 4.0 * r.numel() / ms / 1e6,
-               "frac_of_%s_hbm" % peak_kind: 4.0 * r.numel() / ms / 1e6 / hbm_peak}
+               "frac_of_%s_hbm" % peak_kind: 4.0 * r.numel() / ms / 1e6 / hbm_peak,
+               "cpu_baseline": cpu_rows}
         if gold:
             rec["sha256_equal_reference_cpu"] = (hashlib.sha256(y.cpu().numpy().tobytes()).hexdigest()
                                                  == gold["c3_sum_rows_65536x4096"]["sha256"])
@@ -235,7 +272,7 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
         ms, y = measure(lambda: ops.sum1d(flat))
         rec = {"ms": ms, "GB/s": 4.0 * flat.numel() / ms / 1e6,
                "frac_of_%s_hbm" % peak_kind: 4.0 * flat.numel() / ms / 1e6 / hbm_peak,
-               "elements": flat.numel()}
+               "elements": flat.numel(), "cpu_baseline": cpu_chain}
         if gold and flat.numel() % (1 << 24) == 0:
             want = gold["c3_sum1d_2p30"]["state_after_chunk_hex"][flat.numel() // (1 << 24) - 1]
             rec["bits_equal_reference_cpu"] = (
@@ -312,9 +349,42 @@ def cnn_step_bench(steps, warmup):
     evs[-1].synchronize()
     per = sorted(evs[i].elapsed_time(evs[i + 1]) for i in range(steps))
     ms = per[len(per) // 2]
-    return {"workload": "cnn training step (config 4), batch 256", "ms_per_step": ms,
-            "ms_per_step_mean": evs[0].elapsed_time(evs[-1]) / steps,
-            "GFLOP/s": 18.3 / ms * 1e3, "steps": steps, "parity": parity}
+    rec = {"workload": "cnn training step (config 4), batch 256", "ms_per_step": ms,
+           "ms_per_step_mean": evs[0].elapsed_time(evs[-1]) / steps,
+           "GFLOP/s": 18.3 / ms * 1e3, "steps": steps, "parity": parity}
+    cpu = cnn_step_cpu_reference()
+    if cpu:
+        rec["cpu_baseline"] = cpu
+    return rec
+
+
+def cnn_step_cpu_reference():
+    """One training step of the same model and batch through the reference's own Python layers on its
+    CPU backend (oracle/_ref), timed on the host cores; None where the reference is not built."""
+    import oracle
+    site = oracle.ref_site()
+    if site is None:
+        return None
+    try:
+        if site not in sys.path:
+            sys.path.insert(0, site)
+        import repdl
+        from repdl_b200 import workloads
+        torch.manual_seed(3)
+        model = repdl.from_torch_module(workloads.cnn_torch_model())
+        x, y = workloads.cnn_batch(256)
+        loss_fn = repdl.nn.CrossEntropyLoss()
+        t0 = time.perf_counter()
+        loss = loss_fn(model(x), y)
+        loss.backward()
+        with torch.no_grad():
+            for p in model.parameters():
+                p.add_(p.grad.mul(-0.01))
+        dt = time.perf_counter() - t0
+        return {"value": dt * 1e3, "unit": "ms per step", "cores": torch.get_num_threads(), "kind": "reference",
+                "sample": "one step, batch 256"}
+    except Exception as e:  # the baseline is a report, not part of the measurement
+        return {"unavailable": repr(e)[:200]}
 
 
 def main():
