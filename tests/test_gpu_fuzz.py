@@ -2,6 +2,7 @@
 gradients: padding, strides, ragged tiles, row chunks of every length, rows wider than a chunk;
 products around every tile size; chain sums), each compared bit for bit with the CPU oracle.  The
 oracle itself is pinned to the reference on the fixed cases of tests/cases.py."""
+import os
 import random
 
 import pytest
@@ -10,6 +11,7 @@ import torch
 import oracle
 
 pytestmark = pytest.mark.gpu
+SCALE = int(os.environ.get("REPDL_FUZZ_SCALE", "1"))  # more shapes per run when hunting
 
 
 def bits_equal(a, b):
@@ -45,7 +47,7 @@ def conv_configs(seed, count):
     return out
 
 
-@pytest.mark.parametrize("cfg", conv_configs(20240, 60), ids=lambda c: "x".join(map(str, c[:7])) + "_s%d%d_p%d%d" % (c[7] + c[8]))
+@pytest.mark.parametrize("cfg", conv_configs(20240, 60 * SCALE), ids=lambda c: "x".join(map(str, c[:7])) + "_s%d%d_p%d%d" % (c[7] + c[8]))
 def test_conv_and_gradients_random_shapes(cfg):
     from repdl_b200 import ops
     N, IC, H, W, OC, KH, KW, s, p = cfg
@@ -64,7 +66,7 @@ def mm_shapes(seed, count):
              rnd.random() < 0.5, rnd.random() < 0.5) for _ in range(count)]
 
 
-@pytest.mark.parametrize("shape", mm_shapes(77, 40), ids=lambda s: "%dx%dx%d_%d%d" % s)
+@pytest.mark.parametrize("shape", mm_shapes(77, 40 * SCALE), ids=lambda s: "%dx%dx%d_%d%d" % s)
 def test_mm_random_shapes(shape):
     from repdl_b200 import ops
     M, N, K, ta, tb = shape
@@ -78,7 +80,7 @@ def test_chain_sums_random_shapes():
     from repdl_b200 import ops
     rnd = random.Random(5)
     g = torch.Generator().manual_seed(5)
-    for _ in range(25):
+    for _ in range(25 * SCALE):
         N, C, H, W = rnd.randint(1, 70), rnd.randint(1, 9), rnd.randint(1, 33), rnd.randint(1, 33)
         x = _randn(g, N, C, H, W)
         for avg in (False, True):
