@@ -19,6 +19,16 @@ def bits_equal(a, b):
     return a.shape == b.shape and torch.equal(a.view(torch.int32).reshape(-1), b.view(torch.int32).reshape(-1))
 
 
+def equal_up_to_nan_payload(a, b):
+    """Bit-equal, except that where both hold a NaN the payload may differ (a NaN result of an
+    accumulating operator is NaN on both sides, its payload is outside the contract)."""
+    a, b = a.detach().cpu().contiguous().reshape(-1), b.detach().cpu().contiguous().reshape(-1)
+    if a.shape != b.shape or not torch.equal(torch.isnan(a), torch.isnan(b)):
+        return False
+    keep = ~torch.isnan(b)
+    return torch.equal(a[keep].view(torch.int32), b[keep].view(torch.int32))
+
+
 def _randn(g, *shape):
     # a few exact zeros and a wide range of magnitudes, no non-finite values
     x = torch.randn(*shape, generator=g)
@@ -54,10 +64,20 @@ def test_conv_and_gradients_random_shapes(cfg):
     g = torch.Generator().manual_seed(hash(cfg) & 0xFFFFFF)
     OH, OW = (H + 2 * p[0] - KH) // s[0] + 1, (W + 2 * p[1] - KW) // s[1] + 1
     x, k, go = _randn(g, N, IC, H, W), _randn(g, OC, IC, KH, KW), _randn(g, N, OC, OH, OW)
+    same = bits_equal
+    if (N + IC + H + W + OC) % 4 == 0:
+        # operands that send the zero-padded forms to their exact fallback: values whose products
+        # vanish, and one infinity (which meets exact zeros of the other operand, hence NaNs)
+        for t in (x, k, go):
+            t.view(-1)[1::5] *= 1e-30
+            t.view(-1)[2::11] *= 1e-38
+        x.view(-1)[x.numel() // 2] = float("inf")
+        go.view(-1)[go.numel() // 3] = float("-inf")
+        same = equal_up_to_nan_payload
     xd, kd, god = x.cuda(), k.cuda(), go.cuda()
-    assert bits_equal(ops.conv2d(xd, kd, s, p, 1), oracle.conv2d(x, k, s, p, 1))
-    assert bits_equal(ops.conv2d_grad_input(x.shape, kd, god, s, p), oracle.conv2d_grad_input(x.shape, k, go, s, p))
-    assert bits_equal(ops.conv2d_grad_kernel(xd, k.shape, god, s, p), oracle.conv2d_grad_kernel(x, k.shape, go, s, p))
+    assert same(ops.conv2d(xd, kd, s, p, 1), oracle.conv2d(x, k, s, p, 1))
+    assert same(ops.conv2d_grad_input(x.shape, kd, god, s, p), oracle.conv2d_grad_input(x.shape, k, go, s, p))
+    assert same(ops.conv2d_grad_kernel(xd, k.shape, god, s, p), oracle.conv2d_grad_kernel(x, k.shape, go, s, p))
 
 
 def mm_shapes(seed, count):
