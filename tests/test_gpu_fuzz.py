@@ -109,3 +109,34 @@ def test_chain_sums_random_shapes():
         y = _randn(g, M, K)
         assert bits_equal(ops.sum2d_dim0(y.cuda()), oracle.sum2d_dim0(y)), (M, K)
         assert bits_equal(ops.sum2d_dim1(y.cuda()), oracle.sum2d_dim1(y)), (M, K)
+
+
+def test_sum1d_random_chains():
+    """Long single chains (the summarised path with its opened nodes, tiles and leaves) over element
+    distributions chosen to move the running sum through binades in different ways."""
+    from repdl_b200 import ops
+    rnd = random.Random(11)
+    g = torch.Generator().manual_seed(11)
+    for it in range(24 * SCALE):
+        n = rnd.randint(1 << 16, 1 << 21)
+        kind = it % 8
+        if kind == 0:      # zero-mean: the sum hovers around zero and keeps changing binade
+            x = torch.randn(n, generator=g)
+        elif kind == 1:    # drifting upwards through many binades
+            x = torch.rand(n, generator=g) * 10.0 ** rnd.randint(-3, 3)
+        elif kind == 2:    # heavy tails
+            x = torch.randn(n, generator=g) * torch.exp(3 * torch.randn(n, generator=g))
+        elif kind == 3:    # exact ties: halves of the ulp of the running sum
+            x = torch.randint(-3, 4, (n,), generator=g).float() * 2.0 ** rnd.randint(-30, -10) + 1e-3
+        elif kind == 4:    # a few huge elements among small ones (and a cancellation)
+            x = torch.randn(n, generator=g) * 1e-3
+            idx = torch.randint(0, n, (8,), generator=g)
+            x[idx] = torch.tensor([1e20, -1e20, 3e7, -3e7, 1e30, -1e30, 5e3, -5e3])
+        elif kind == 5:    # subnormal and tiny values
+            x = torch.randn(n, generator=g) * 1e-40
+        elif kind == 6:    # constant: the sum saturates where the element is below half an ulp
+            x = torch.full((n,), rnd.choice([1.0, 0.1, 3.0e-5]))
+        else:              # sign flips in blocks
+            x = torch.rand(n, generator=g) * torch.sign(torch.sin(torch.arange(n) / rnd.randint(50, 50000)))
+        for avg in (False, True):
+            assert bits_equal(ops.sum1d(x.cuda(), avg), oracle.sum1d(x, avg)), (it, kind, n)
