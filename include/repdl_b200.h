@@ -81,6 +81,17 @@ int repdl_b200_conv2d_grad_kernel(const float *grad_output, const float *input,
                                   int64_t W, int64_t OC, int64_t KH, int64_t KW, int64_t sH,
                                   int64_t sW, int64_t pH, int64_t pW, void *stream);
 
+/* The weight gradient and the bias gradient of one convolution in one pass over grad_output:
+ * replaces the pair of calls in Conv2dFunction.backward, repdl/nn/conv.py:45-50
+ * (ops.conv2d_grad_kernel, then ops.sum4d_dim023(grad_output)); grad_bias[oc] is the chain over
+ * n, oh, ow of backend/cpu/summation.cpp (sum4d_dim023, no averaging), bit for bit.  Offered for the
+ * shapes the row-chunk kernel takes (at least 256 chain steps and output rows of a useful length);
+ * REPDL_E_UNSUPPORTED otherwise, and the caller makes the two separate calls. */
+int repdl_b200_conv2d_grad_kernel_bias(const float *grad_output, const float *input,
+                                       float *grad_kernel, float *grad_bias, int64_t N, int64_t IC,
+                                       int64_t H, int64_t W, int64_t OC, int64_t KH, int64_t KW,
+                                       int64_t sH, int64_t sW, int64_t pH, int64_t pW, void *stream);
+
 /* ---- fixed-order sums --------------------------------------------------------------------
  * Replace repdl::cuda::summation::{sum1d, sum2d_dim0, sum2d_dim1, sum4d_dim023}
  * (backend/cuda/summation.cu:33-43, 59-71, 94-105, 132-144); bits defined by

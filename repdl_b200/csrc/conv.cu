@@ -679,10 +679,13 @@ struct GkChunk {
 };
 
 // RW x CB multiplying warps, each owning a patch of 4 output channels x 8 weight columns.
-template <bool PADDED, int RW, int CB>
+// BIAS: the CTAs of the first column block also add up their rows of grad_output -- the row operand
+// the chains consume anyway, in the order n, oh, ow of the reference's sum4d_dim023 -- and write the
+// bias gradient, which saves the separate pass over grad_output.
+template <bool PADDED, int RW, int CB, bool BIAS>
 __global__ void __launch_bounds__((RW * CB) * 32 + GKR_STAGERS)
 conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, float *__restrict__ GK,
-                    ConvDims d, int segW, int R, int a16, long long nchunks)
+                    float *__restrict__ GB, ConvDims d, int segW, int R, int a16, long long nchunks)
 {
     extern __shared__ __align__(16) float gkr_smem[];
     constexpr int ROWS = 4 * RW, COLS = 8 * CB, NCW = RW * CB;
@@ -712,7 +715,8 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
     GkChunk cur = {0, 0, 0};
     int stage = 0;  // stage of chunk ci; the chunk issued in iteration ci goes to the stage before it
     bool unsafe = false;
-    float acc = 0.0f;
+    float acc = 0.0f, accb = 0.0f;
+    const bool do_bias = BIAS && blockIdx.x == 0;
     // Multiplying role: which output of the CTA's tile a thread owns.  Shared memory serves a 16-byte
     // load eight lanes at a time, and passes of one load that fetch the same addresses in the same
     // lanes are merged.  So the lanes of a warp's 4 x 8 patch are laid out with all four rows in
@@ -843,6 +847,12 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
                     acc = __fmaf_rn(a[i].y, b[i].y, acc);
                     acc = __fmaf_rn(a[i].z, b[i].z, acc);
                     acc = __fmaf_rn(a[i].w, b[i].w, acc);
+                    if (do_bias) {
+                        accb = __fadd_rn(accb, a[i].x);
+                        accb = __fadd_rn(accb, a[i].y);
+                        accb = __fadd_rn(accb, a[i].z);
+                        accb = __fadd_rn(accb, a[i].w);
+                    }
                 }
             };
             if (ng > 0) load(aA, bA, 0);
@@ -860,9 +870,18 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
                 acc = __fmaf_rn(a.y, b.y, acc);
                 acc = __fmaf_rn(a.z, b.z, acc);
                 acc = __fmaf_rn(a.w, b.w, acc);
+                if (do_bias) {
+                    accb = __fadd_rn(accb, a.x);
+                    accb = __fadd_rn(accb, a.y);
+                    accb = __fadd_rn(accb, a.z);
+                    accb = __fadd_rn(accb, a.w);
+                }
             }
             const float *as = reinterpret_cast<const float *>(ar), *bs = reinterpret_cast<const float *>(br);
-            for (int k = 4 * k4; k < len; k++) acc = __fmaf_rn(as[k], bs[k], acc);
+            for (int k = 4 * k4; k < len; k++) {
+                acc = __fmaf_rn(as[k], bs[k], acc);
+                if (do_bias) accb = __fadd_rn(accb, as[k]);
+            }
         };
         for (long long ci = 0; ci < nchunks; ci++) {
             chunk_barrier();
@@ -882,17 +901,18 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
             }
             GK[(int64_t)oc * ncols + col] = v;
         }
+        if (do_bias && ccol == 0 && oc < d.OC) GB[oc] = accb;
     }
 }
 
-template <bool PADDED, int RW, int CB>
-int launch_gk_rows(const float *go, const float *in, float *gk, const ConvDims &d, int segW, int R,
-                   cudaStream_t st)
+template <bool PADDED, int RW, int CB, bool BIAS>
+int launch_gk_rows(const float *go, const float *in, float *gk, float *gb, const ConvDims &d, int segW,
+                   int R, cudaStream_t st)
 {
     static unsigned long long done = 0;
     constexpr int ROWS = 4 * RW, COLS = 8 * CB;
     constexpr int SMEM = GKR_STAGES * (ROWS + COLS) * GKR_PITCH * (int)sizeof(float);
-    int e = ensure_smem(conv_gk_rows_kernel<PADDED, RW, CB>, SMEM, &done);
+    int e = ensure_smem(conv_gk_rows_kernel<PADDED, RW, CB, BIAS>, SMEM, &done);
     if (e) return e;
     const int ncols = d.IC * d.KH * d.KW;
     const long long nchunks = (long long)d.N * ((d.OH + R - 1) / R) * ((d.OW + segW - 1) / segW);
@@ -901,25 +921,25 @@ int launch_gk_rows(const float *go, const float *in, float *gk, const ConvDims &
     const bool a16 = ((uintptr_t)go % 16 == 0) && ((int64_t)d.OH * d.OW % 4 == 0) &&
                      (segW == d.OW ? ((int64_t)R * d.OW % 4 == 0) : (d.OW % 4 == 0));
     dim3 grid((unsigned)((ncols + COLS - 1) / COLS), (unsigned)((d.OC + ROWS - 1) / ROWS));
-    conv_gk_rows_kernel<PADDED, RW, CB><<<grid, RW * CB * 32 + GKR_STAGERS, SMEM, st>>>(
-        go, in, gk, d, segW, R, a16 ? 1 : 0, nchunks);
+    conv_gk_rows_kernel<PADDED, RW, CB, BIAS><<<grid, RW * CB * 32 + GKR_STAGERS, SMEM, st>>>(
+        go, in, gk, gb, d, segW, R, a16 ? 1 : 0, nchunks);
     return launch_status();
 }
 
 // few outputs: patches of 4 x 8 (one multiplying warp per CTA) put them on four times as many SMs
-int launch_gk_rows_any(const float *go, const float *in, float *gk, const ConvDims &d, int segW, int R,
-                       cudaStream_t st)
+template <bool BIAS>
+int launch_gk_rows_any(const float *go, const float *in, float *gk, float *gb, const ConvDims &d, int segW,
+                       int R, cudaStream_t st)
 {
     const int ncols = d.IC * d.KH * d.KW;
     const bool padded = (d.pH | d.pW) != 0;
     const int64_t big_tiles = (int64_t)((ncols + 15) / 16) * ((d.OC + 7) / 8);
     if (2 * big_tiles < sm_count())
-        return padded ? launch_gk_rows<true, 1, 1>(go, in, gk, d, segW, R, st)
-                      : launch_gk_rows<false, 1, 1>(go, in, gk, d, segW, R, st);
-    return padded ? launch_gk_rows<true, 2, 2>(go, in, gk, d, segW, R, st)
-                  : launch_gk_rows<false, 2, 2>(go, in, gk, d, segW, R, st);
+        return padded ? launch_gk_rows<true, 1, 1, BIAS>(go, in, gk, gb, d, segW, R, st)
+                      : launch_gk_rows<false, 1, 1, BIAS>(go, in, gk, gb, d, segW, R, st);
+    return padded ? launch_gk_rows<true, 2, 2, BIAS>(go, in, gk, gb, d, segW, R, st)
+                  : launch_gk_rows<false, 2, 2, BIAS>(go, in, gk, gb, d, segW, R, st);
 }
-
 
 int fill_dims(ConvDims &d, int64_t N, int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH,
               int64_t KW, int64_t sH, int64_t sW, int64_t pH, int64_t pW, int64_t groups)
@@ -1004,11 +1024,12 @@ extern "C" int repdl_b200_conv2d_grad_input(const float *grad_output, const floa
     return launch_status();
 }
 
-extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const float *input,
-                                             float *grad_kernel, int64_t N, int64_t IC, int64_t H,
-                                             int64_t W, int64_t OC, int64_t KH, int64_t KW,
-                                             int64_t sH, int64_t sW, int64_t pH, int64_t pW,
-                                             void *stream)
+// grad_bias != nullptr: the fused form, which only the row-chunk kernel offers (REPDL_E_UNSUPPORTED
+// for shapes that take another kernel: the caller then uses the two separate entry points).
+static int conv2d_grad_kernel_impl(const float *grad_output, const float *input, float *grad_kernel,
+                                   float *grad_bias, int64_t N, int64_t IC, int64_t H, int64_t W,
+                                   int64_t OC, int64_t KH, int64_t KW, int64_t sH, int64_t sW, int64_t pH,
+                                   int64_t pW, void *stream)
 {
     clear_stale_error();
     ConvDims d;
@@ -1034,8 +1055,12 @@ extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const flo
             }
         if ((d.OC + 3) / 4 <= 65535 && (int64_t)R * segW >= 64 && d.KH < 32768 && d.KW < 32768 &&
             (int64_t)d.OH * d.OW < (1 << 30) && ((int64_t)d.H + 2 * d.pH) * d.W < (1 << 30)) {
-            return launch_gk_rows_any(grad_output, input, grad_kernel, d, segW, R, (cudaStream_t)stream);
+            return grad_bias ? launch_gk_rows_any<true>(grad_output, input, grad_kernel, grad_bias, d, segW,
+                                                        R, (cudaStream_t)stream)
+                             : launch_gk_rows_any<false>(grad_output, input, grad_kernel, nullptr, d, segW,
+                                                         R, (cudaStream_t)stream);
         }
+        if (grad_bias) return REPDL_E_UNSUPPORTED;
         if (gy <= 65535 && d.OW < 65536 && (int64_t)d.OH * d.OW < (1 << 24)) {
             if (narrow)
                 conv_gk_kernel<16><<<dim3((unsigned)((ncols + 15) / 16), gy), GK_THREADS, 0,
@@ -1046,9 +1071,31 @@ extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const flo
             return launch_status();
         }
     }
+    if (grad_bias) return REPDL_E_UNSUPPORTED;
     unsigned blocks;
     if ((e = blocks_for(total, blocks))) return e;
     conv2d_grad_kernel_direct_kernel<<<blocks, CONV_THREADS, 0, (cudaStream_t)stream>>>(
         grad_output, input, grad_kernel, d, total);
     return launch_status();
+}
+
+extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const float *input,
+                                             float *grad_kernel, int64_t N, int64_t IC, int64_t H,
+                                             int64_t W, int64_t OC, int64_t KH, int64_t KW,
+                                             int64_t sH, int64_t sW, int64_t pH, int64_t pW,
+                                             void *stream)
+{
+    return conv2d_grad_kernel_impl(grad_output, input, grad_kernel, nullptr, N, IC, H, W, OC, KH, KW, sH,
+                                   sW, pH, pW, stream);
+}
+
+extern "C" int repdl_b200_conv2d_grad_kernel_bias(const float *grad_output, const float *input,
+                                                  float *grad_kernel, float *grad_bias, int64_t N,
+                                                  int64_t IC, int64_t H, int64_t W, int64_t OC,
+                                                  int64_t KH, int64_t KW, int64_t sH, int64_t sW,
+                                                  int64_t pH, int64_t pW, void *stream)
+{
+    if (!grad_bias) return REPDL_E_NULL;
+    return conv2d_grad_kernel_impl(grad_output, input, grad_kernel, grad_bias, N, IC, H, W, OC, KH, KW,
+                                   sH, sW, pH, pW, stream);
 }

@@ -96,6 +96,26 @@ def conv2d_grad_kernel(input, weight_shape, grad_output, stride, padding) -> tor
     return out
 
 
+def conv2d_grad_kernel_bias(input, weight_shape, grad_output, stride, padding):
+    """(conv2d_grad_kernel, sum4d_dim023(grad_output)) from one pass over grad_output, or None when
+    the shape is not one the fused kernel takes (the caller then makes the two calls)."""
+    _need(input, "input", 4), _need(grad_output, "grad_output", 4)
+    x, go = input.contiguous(), grad_output.contiguous()
+    N, IC, H, W = x.shape
+    OC = go.shape[1]
+    KH, KW = int(weight_shape[2]), int(weight_shape[3])
+    gw = torch.empty((OC, IC, KH, KW), dtype=torch.float32, device=x.device)
+    gb = torch.empty((OC,), dtype=torch.float32, device=x.device)
+    with torch.cuda.device(x.device):
+        status = lib.repdl_b200_conv2d_grad_kernel_bias(go.data_ptr(), x.data_ptr(), gw.data_ptr(),
+                                                        gb.data_ptr(), N, IC, H, W, OC, KH, KW, stride[0],
+                                                        stride[1], padding[0], padding[1], _stream(x))
+    if status == -5:  # REPDL_E_UNSUPPORTED
+        return None
+    check(status, "conv2d_grad_kernel_bias")
+    return gw, gb
+
+
 def _factor(average, count):
     # backend/cpu/summation.cpp:15: float factor = average ? 1.0 / N : 1.0 (double division, then fp32)
     import numpy as np

@@ -77,7 +77,12 @@ def test_conv_and_gradients_random_shapes(cfg):
     xd, kd, god = x.cuda(), k.cuda(), go.cuda()
     assert same(ops.conv2d(xd, kd, s, p, 1), oracle.conv2d(x, k, s, p, 1))
     assert same(ops.conv2d_grad_input(x.shape, kd, god, s, p), oracle.conv2d_grad_input(x.shape, k, go, s, p))
-    assert same(ops.conv2d_grad_kernel(xd, k.shape, god, s, p), oracle.conv2d_grad_kernel(x, k.shape, go, s, p))
+    want_gk = oracle.conv2d_grad_kernel(x, k.shape, go, s, p)
+    assert same(ops.conv2d_grad_kernel(xd, k.shape, god, s, p), want_gk)
+    fused = ops.conv2d_grad_kernel_bias(xd, k.shape, god, s, p)  # None: shape not taken by the fused kernel
+    if fused is not None:
+        assert same(fused[0], want_gk)
+        assert same(fused[1].reshape(-1), oracle.sum4d_dim023(go).reshape(-1))
 
 
 def mm_shapes(seed, count):
