@@ -5,10 +5,13 @@
 // loop order; taps that fall into the padding are SKIPPED (not multiplied by zero -- a zero
 // product would turn an accumulator of -0 into +0 and a non-finite weight into NaN).
 //
-// Two forms live in this file.
+// Three forms live in this file.
 //   direct : one thread owns one output element and walks its chain exactly as the reference's
-//            loops do (always exact; used for conv2d_grad_kernel, for kernels with more than 64
-//            taps and as the per-tile fallback of the other form);
+//            loops do (always exact; used for kernels with more than 64 taps, for gradients with
+//            very short chains and as the per-tile fallback of the other forms);
+//   chains : conv2d_grad_kernel -- few outputs, each a chain over batch x OH x OW steps: warps that
+//            only multiply (one chain per thread) fed by warps that only stage operands into shared
+//            memory, see the two kernels further down; optionally with the bias gradient fused in;
 //   GEMM   : conv2d and conv2d_grad_input as an implicit GEMM on the FP32 FMA pipe -- the same
 //            register-blocked main loop as mm (8 x 8 outputs per thread, K in slabs of 16 through
 //            double-buffered shared memory), with the im2col matrix gathered on the fly.  A tap that
