@@ -212,6 +212,25 @@ def run_reference(args, rank):
     print(json.dumps(line), flush=True)
 
 
+def sum1d_walk_stats(flat):
+    """What the serial part of the chain sum had to do (the walker's counters, read back from the
+    scratch buffer of one extra call)."""
+    import ctypes
+    from repdl_b200._cabi import check, lib
+    nb = lib.repdl_b200_sum1d_scratch_bytes(flat.numel())
+    if nb == 0:
+        return None
+    sc = torch.empty(nb, dtype=torch.uint8, device=flat.device)
+    o = torch.zeros((), device=flat.device)
+    check(lib.repdl_b200_sum1d(flat.data_ptr(), o.data_ptr(), flat.numel(), 1.0, sc.data_ptr(), nb, None), "sum1d")
+    torch.cuda.synchronize()
+    st = (ctypes.c_longlong * 12)()
+    check(lib.repdl_b200_sum1d_stats(sc.data_ptr(), st), "sum1d_stats")
+    names = ["items", "summaries_applied", "leaves_walked", "spans_walked", "leaves_in_spans",
+             "soft_runs_not_valid", "robust_runs_not_valid"]
+    return dict(zip(names, list(st)[:7]), scratch_bytes=nb)
+
+
 def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
     """The HBM-bound kernels (configs 2 and 3) with their own rooflines, on one GPU.  At the full
     size (2^28 elements) the outputs are also hashed and compared with the reference's hashes."""
@@ -277,24 +296,7 @@ def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
             want = gold["c3_sum1d_2p30"]["state_after_chunk_hex"][flat.numel() // (1 << 24) - 1]
             rec["bits_equal_reference_cpu"] = (
                 "%08x" % (y.cpu().view(torch.int32).item() & 0xFFFFFFFF)) == want
-        # how the walk went: opened nodes / tiles / leaves (and, in a build with clocks, the walker's
-        # cycle counters), which the kernel leaves in the first bytes of its scratch buffer
-        from repdl_b200._cabi import check, lib
-        nb = lib.repdl_b200_sum1d_scratch_bytes(flat.numel())
-        if nb >= 80:
-            sc = torch.zeros(nb, dtype=torch.uint8, device=flat.device)
-            o = torch.zeros((), device=flat.device)
-            check(lib.repdl_b200_sum1d(flat.data_ptr(), o.data_ptr(), flat.numel(), 1.0, sc.data_ptr(), nb, None),
-                  "sum1d")
-            torch.cuda.synchronize()
-            opens = sc[:16].view(torch.int32).tolist()
-            cyc = sc[16:64].view(torch.int64).tolist()
-            rec["walk"] = {"nodes": opens[3], "opened_nodes": opens[0], "opened_tiles": opens[1],
-                           "opened_leaves": opens[2]}
-            if cyc[0]:  # only a library built with -DREPDL_SUM1D_CLOCKS=1 counts cycles
-                rec["walk"].update({"cycles_total": cyc[0], "cycles_prepare_nodes": cyc[1],
-                                    "cycles_leaf_level": cyc[2], "cycles_leaf_adds": cyc[3],
-                                    "cycles_leaf_rebuild": cyc[4]})
+        rec["walk"] = sum1d_walk_stats(flat)
         out["sum1d chain [%d]" % flat.numel()] = rec
     return out
 

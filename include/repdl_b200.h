@@ -99,24 +99,33 @@ int repdl_b200_conv2d_grad_kernel_bias(const float *grad_output, const float *in
  * +0, multiplied once by `factor` at the end (1.0f, or float(1.0/count) for a mean).
  *
  * sum1d reproduces one chain of n elements without walking it element by element (per-binade
- * integer summaries, see csrc/sum1d.cu).  It needs scratch: pass a buffer of at least
- * repdl_b200_sum1d_scratch_bytes(n) bytes (0 for short chains; about n/600 bytes otherwise),
+ * integer summaries prepared in parallel, applied by one thread after an exact validity check;
+ * see csrc/sum1d.cu).  It needs scratch: pass a buffer of at least
+ * repdl_b200_sum1d_scratch_bytes(n) bytes (0 for short chains; about 1 MB + n/30 bytes otherwise),
  * 256-byte aligned; its contents on entry do not matter and it may be reused by the next call
- * on the same stream (calls that overlap on the GPU must not share it). */
+ * on the same stream (calls that overlap on the GPU must not share it).  n is limited to
+ * 2^36 - 2^15 elements (REPDL_E_RANGE beyond). */
 size_t repdl_b200_sum1d_scratch_bytes(int64_t n);
 int repdl_b200_sum1d(const float *x, float *out, int64_t n, float factor, void *scratch,
                      size_t scratch_bytes, void *stream);
+/* Diagnostics (no counterpart in the reference): what the walker of the last finished long-chain
+ * call on `scratch` did.  stats must hold 12 values: [0..7) = items in the stream, summaries applied, leaves walked with
+ * real adds, spans walked with real adds, leaves in those spans, composed soft runs that did not
+ * fit the exact state, composed robust runs that did not fit; [7..12) = cycle counters of the walker
+ * thread (zero unless the library was built with -DREPDL_SUM1D_CLOCKS=1).  Synchronous (one small copy). */
+int repdl_b200_sum1d_stats(const void *scratch, long long *stats);
 /* The same chain sum for callers that cannot allocate device memory at all.  (No counterpart in
  * the reference.)  Some hosts of this library are not allowed to call cudaMalloc or to go through
  * an allocating framework on the path that needs the sum: code running inside a CUDA-graph capture,
  * real-time or interrupt-like callbacks, a process whose memory pool is owned and fully handed out
  * by someone else, or a plugin ABI that only passes inputs and outputs.  For them the scratch of
- * repdl_b200_sum1d lives in a fixed array inside this library's device image (about 1.5 MB, held by
+ * repdl_b200_sum1d lives in a fixed array inside this library's device image (about 10 MB, held by
  * every GPU that loads the library until the process exits), so the caller passes only x and out.
- *   - n may be at most repdl_b200_sum1d_static_max_n() (2^30 elements); a longer chain returns
+ *   - n may be at most repdl_b200_sum1d_static_max_n() (2^28 elements); a longer chain returns
  *     REPDL_E_STATIC_MAX and does nothing.
- *   - The first call on each device looks up the array's device address (cudaGetSymbolAddress, with
- *     that device current).  Make that first call before starting any stream capture.
+ *   - The first call on each device, whatever its n, looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current) and sets a kernel attribute.  Make that
+ *     first call before starting any stream capture.
  *   - Every call on a device shares the one array and it keeps the previous call's contents.
  *     Nothing in it has to be cleared (each call writes every word before reading it), but two calls
  *     whose kernels can overlap on the GPU (different streams) race on it: serialise them.

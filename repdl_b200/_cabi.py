@@ -28,6 +28,7 @@ SIGNATURES = {
     "repdl_b200_conv2d_grad_kernel_bias": (_int, [_ptr, _ptr, _ptr, _ptr] + [_i64] * 11 + [_ptr]),
     "repdl_b200_sum1d_scratch_bytes": (_size, [_i64]),
     "repdl_b200_sum1d": (_int, [_ptr, _ptr, _i64, _f32, _ptr, _size, _ptr]),
+    "repdl_b200_sum1d_stats": (_int, [_ptr, _ptr]),
     "repdl_b200_sum1d_static_max_n": (_i64, []),
     "repdl_b200_sum1d_static": (_int, [_ptr, _ptr, _i64, _f32, _ptr]),
     "repdl_b200_sum2d_dim0": (_int, [_ptr, _ptr, _i64, _i64, _f32, _ptr]),

@@ -54,6 +54,14 @@ __device__ __forceinline__ void cp_async_16(void *smem_dst, const void *gmem_src
     unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(d), "l"(gmem_src) : "memory");
 }
+// 4-byte global -> shared copy; copies nothing and writes zero when `valid` is false (the source
+// address must still be a mapped one).
+__device__ __forceinline__ void cp_async_4_zfill(void *smem_dst, const void *gmem_src, bool valid)
+{
+    unsigned d = (unsigned)__cvta_generic_to_shared(smem_dst);
+    int sz = valid ? 4 : 0;
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4, %2;" ::"r"(d), "l"(gmem_src), "r"(sz) : "memory");
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N>
 __device__ __forceinline__ void cp_async_wait()

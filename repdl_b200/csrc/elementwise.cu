@@ -66,21 +66,15 @@ struct OpLog {
     }
     __device__ __forceinline__ float slow(float x) const { return crm_log_slow(x); }
 };
-// x / d for one divisor d: (float)((double)x * rd) with rd = 1.0 / (double)d.  The product is within
-// 2^-52 (relative) of the exact quotient, and the quotient of two fp32 values stays at least 2^-49
-// (relative) away from every fp32 rounding midpoint (|a/b - c/2^j| >= 1/(b 2^j) for 24-bit a, b and
-// odd c), so the double rounding cannot change the result: this IS the IEEE fp32 quotient, with no
-// slow path for extreme exponents.  (Checked against x / d for all 2^32 x and a dozen divisors on
-// the CPU.)  Only NaN results take the branch, for the x86 payload rules of cr_div.
+// x / d for one divisor d (cr_div_by_reciprocal: one fp64 multiply, exact division only for
+// subnormal and NaN results).
 struct OpDivScalar {
     static constexpr bool kTables = false;
     float d;
     double rd;
     __device__ __forceinline__ float fast(float x, SmemTables, bool &slow) const
     {
-        const float q = __double2float_rn(__dmul_rn((double)x, rd));
-        slow = q != q;
-        return q;
+        return cr_div_by_reciprocal(x, rd, slow);
     }
     __device__ __forceinline__ float slow(float x) const { return cr_div(x, d); }
 };

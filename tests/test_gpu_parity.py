@@ -148,6 +148,21 @@ def test_sqrt_sweep_of_the_input_domain(ops):
         assert bits_equal(ops.sqrt(x.cuda()), oracle.sqrt(x))
 
 
+def test_scalar_division_with_subnormal_quotients(ops):
+    """x / d for divisors whose quotients reach rounding midpoints of the subnormal range (the
+    kernel multiplies by a double reciprocal and must fall back to the exact division there):
+    every x bit pattern below 2^26 (all quotients subnormal or tiny), both signs, and a strided
+    sweep of the whole domain."""
+    low = torch.arange(0, 1 << 26, dtype=torch.int64)
+    wide = torch.arange(0, 1 << 32, 4093, dtype=torch.int64)
+    for d in (98.0, 150.0, 154.0, 182.0, -186.0, 198.0, 10.0):
+        for b in (low, low | 0x80000000, wide):
+            x = (b & 0xFFFFFFFF).to(torch.uint32).view(torch.float32)
+            assert bits_equal(ops.div(x.cuda(), d), oracle.div(x, d)), d
+    x = torch.tensor([147 * 2.0 ** -149], dtype=torch.float32)  # 1.5 ulp: ties to even
+    assert ops.div(x.cuda(), 98.0).cpu().view(torch.int32).item() == 2
+
+
 def test_mm_from_host_pipeline_equals_one_launch(ops):
     """The pipelined host-operand step (row blocks uploaded, multiplied and downloaded on three
     streams) gives the bits of the one-launch product, twice in a row on the same buffers."""

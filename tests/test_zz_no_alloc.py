@@ -47,11 +47,24 @@ def test_static_scratch_sum_matches_caller_scratch_sum_twice_in_a_row():
     b = (torch.empty(1500000).log_normal_(0, 2, generator=g)
          * (torch.randint(0, 2, (1500000,), generator=g).float() * 2 - 1))
     ad, bd = a.cuda(), b.cuda()
-    for x, factor in ((ad, 1.0), (bd, 0.5), (ad, 1.0)):
+    import oracle
+    _static(lib, check, ad, 1.0)  # the set-up call: later calls must not change the device's memory
+    torch.cuda.synchronize()
+    for x, xc, factor in ((ad, a, 1.0), (bd, b, 0.5), (ad, a, 1.0)):
         want = _with_scratch(lib, check, x, factor)
-        got = _static(lib, check, x, factor)
         torch.cuda.synchronize()
-        assert _bits(got) == _bits(want)
+        free0, held0 = torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated()
+        out = torch.empty((), dtype=torch.float32, device=x.device)  # the caller's own output buffer
+        held1 = torch.cuda.memory_allocated()
+        check(lib.repdl_b200_sum1d_static(x.data_ptr(), out.data_ptr(), x.numel(), factor, None),
+              "sum1d_static")
+        torch.cuda.synchronize()
+        # no allocation behind the caller's back: neither torch's pool nor the device's free memory moved
+        assert torch.cuda.memory_allocated() == held1 and torch.cuda.mem_get_info()[0] == free0, (free0, held0)
+        assert _bits(out) == _bits(want)
+        # ... and both are the reference's chain (the oracle's strict left-to-right sum)
+        scaled = oracle.sum1d(xc, False) * factor  # factor 0.5 / 1.0: an exact scaling
+        assert _bits(out) == _bits(scaled)
     # a short chain takes the scratch-free path of both entry points
     s = ad[:1000].contiguous()
     assert _bits(_static(lib, check, s, 1.0)) == _bits(_with_scratch(lib, check, s, 1.0))
@@ -60,7 +73,7 @@ def test_static_scratch_sum_matches_caller_scratch_sum_twice_in_a_row():
 def test_static_scratch_sum_rejects_chains_beyond_its_maximum():
     from repdl_b200._cabi import lib
     max_n = lib.repdl_b200_sum1d_static_max_n()
-    assert max_n == 1 << 30
+    assert max_n == 1 << 28
     x = torch.zeros(16, device="cuda")
     out = torch.zeros((), device="cuda")
     # the size check comes before any memory access, so a small buffer is enough to probe it
