@@ -30,6 +30,25 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
+
+def _reference_arm_requested(argv):
+    for i, a in enumerate(argv):
+        if a == "--impl" and i + 1 < len(argv) and argv[i + 1] == "reference":
+            return True
+        if a == "--impl=reference":
+            return True
+    return False
+
+
+if _reference_arm_requested(sys.argv):
+    # The reference arm is the reference's OpenMP loop on the host cores.  Only rank 0 runs it, and
+    # it must get every core: torch.distributed.run exports OMP_NUM_THREADS=1 to its workers, and
+    # both OpenMP runtimes (torch's and the libgomp the reference extension links) read the
+    # variable when they are loaded, i.e. before `import torch`.
+    if int(os.environ.get("RANK", "0")) != 0:
+        sys.exit(0)
+    os.environ["OMP_NUM_THREADS"] = str(os.cpu_count() or 1)
+
 import torch  # noqa: E402
 
 
@@ -181,17 +200,27 @@ def time_cpu_mm(a, b, budget_s, rows0=4):
 
 
 def run_reference(args, rank):
-    """--impl reference: the reference's own CPU implementation of the path, rank 0 only."""
+    """--impl reference: the reference's own CPU implementation of the path, rank 0 only.  Each step
+    multiplies a fixed sample of rows of A with the full B; the sample is shrunk, if need be, so that
+    the whole run of warm-up and timed steps stays within --ref-budget seconds."""
     if rank != 0:
         return
     from repdl_b200 import workloads
     n = args.size
     a, b = workloads.mm_large(n, 4)
     kind, fn, cores = load_reference_cpu()
-    rows = args.ref_rows
+    torch.set_num_threads(os.cpu_count() or 1)
+    cores = max(cores, torch.get_num_threads())
+    # one probe row block decides how many rows a step can afford
+    probe = min(4, args.ref_rows)
+    t = time.perf_counter()
+    fn(a[:probe].contiguous(), b, False, False)
+    per_row = (time.perf_counter() - t) / probe
+    calls = args.steps + args.warmup
+    rows = int(max(1, min(args.ref_rows, args.ref_budget / max(calls, 1) / max(per_row, 1e-6))))
     sample = a[:rows].contiguous()
     for _ in range(args.warmup):
-        fn(sample[:max(1, rows // 4)], b, False, False)
+        fn(sample, b, False, False)
     t = time.perf_counter()
     for _ in range(args.steps):
         fn(sample, b, False, False)
@@ -229,6 +258,170 @@ def sum1d_walk_stats(flat):
     names = ["items", "summaries_applied", "leaves_walked", "spans_walked", "leaves_in_spans",
              "soft_runs_not_valid", "robust_runs_not_valid"]
     return dict(zip(names, list(st)[:7]), scratch_bytes=nb)
+
+
+def flush_l2(scratch):
+    """Evicts the 126 MB L2 between timed iterations of a workload that would otherwise fit in it."""
+    scratch.add_(1.0)
+
+
+def extras_mm(peak_tflops):
+    """Config 1 (M = N = K = 1024, seed 0) and a mid size (4096), each launch timed on its own with
+    CUDA events.  Config 1's operands and result are 12 MiB and fit the L2, so the L2 is flushed
+    between timed launches (a 256 MiB buffer is rewritten); the L2-warm time is reported next to it."""
+    from repdl_b200 import ops, workloads
+    import oracle
+    out = {}
+    gold_path = os.path.join(ROOT, "tests", "golden", "configs.json")
+    gold = json.load(open(gold_path)) if os.path.exists(gold_path) else None
+    scratch = torch.zeros(64 << 20, device="cuda")  # 256 MiB
+    for n, seed, name in ((1024, 0, "mm 1024^3 (config 1)"), (4096, 0, "mm 4096^3")):
+        a, b = workloads.mm_square(n, seed)
+        ad, bd = a.cuda(), b.cuda()
+        for _ in range(3):
+            c = ops.mm(ad, bd)
+        torch.cuda.synchronize()
+        cold = []
+        for _ in range(7):
+            flush_l2(scratch)
+            cold.append(event_ms(lambda: ops.mm(ad, bd)))
+        warm = min(event_ms(lambda: ops.mm(ad, bd)) for _ in range(5))
+        cold.sort()
+        ms = cold[len(cold) // 2]
+        tf = 2.0 * n ** 3 / ms / 1e9
+        rec = {"ms": ms, "ms_l2_warm": warm, "TFLOP/s": tf, "frac_of_ffma_peak": tf / peak_tflops,
+               "frac_of_nominal": tf / (148 * 128 * 2 * 1.965e9 / 1e12),
+               "l2": "flushed between timed launches" if n == 1024 else "operands (192 MiB) exceed L2; also flushed"}
+        if n == 1024 and gold:
+            rec["sha256_equal_reference_cpu"] = (
+                hashlib.sha256(c.cpu().numpy().tobytes()).hexdigest() == gold["c1_mm_1024"]["sha256"])
+        if n == 4096:
+            rows = 32  # the CPU oracle on a row sample (the whole product would take half a minute)
+            rec["rows_0_32_equal_oracle"] = bool(torch.equal(
+                c[:rows].cpu().view(torch.int32), oracle.mm(a[:rows].contiguous(), b).view(torch.int32)))
+        out[name] = rec
+        del ad, bd, c
+    return out
+
+
+def extras_sum1d_full(hbm_peak, peak_kind, steps=5, warmup=3):
+    """Config 3's 1-D case at its full size: ONE chain over 2^30 elements (4 GiB)."""
+    from repdl_b200 import ops, workloads
+    n = 1 << 30
+    x = torch.empty(n, device="cuda")
+    o = 0
+    for c in workloads.sum_chunks(n, 2):
+        x[o:o + c.numel()] = c.cuda()
+        o += c.numel()
+    for _ in range(warmup):
+        y = ops.sum1d(x)
+    torch.cuda.synchronize()
+    ms = min(event_ms(lambda: ops.sum1d(x)) for _ in range(steps))
+    rec = {"ms": ms, "GB/s": 4.0 * n / ms / 1e6, "frac_of_%s_hbm" % peak_kind: 4.0 * n / ms / 1e6 / hbm_peak,
+           "elements": n, "walk": sum1d_walk_stats(x)}
+    gold_path = os.path.join(ROOT, "tests", "golden", "configs.json")
+    if os.path.exists(gold_path):
+        want = json.load(open(gold_path))["c3_sum1d_2p30"]["result_hex"]
+        rec["bits_equal_reference_cpu"] = ("%08x" % (y.cpu().view(torch.int32).item() & 0xFFFFFFFF)) == want
+    del x
+    torch.cuda.empty_cache()
+    return rec
+
+
+def reference_cuda_bench():
+    """The reference's OWN CUDA backend (backend/cuda/*, compiled unmodified for sm_100a into
+    oracle/_ref by oracle/build_ref.sh) on the same inputs, timed with CUDA events: the existing GPU
+    kernels this repository replaces.  Every result is also compared with the CPU backend's bits
+    (golden hashes, or this repository's result where that has just been checked against them).
+    Returns None where the reference is not built."""
+    import glob
+    import importlib.util
+    import oracle
+    from repdl_b200 import ops, workloads
+    site = oracle.ref_site()
+    cands = glob.glob(os.path.join(site, "repdl", "backend", "cuda*.so")) if site else []
+    if not cands:
+        return None
+    spec = importlib.util.spec_from_file_location("cuda", cands[0])
+    rc = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(rc)
+    rmath = None
+    mpath = os.path.join(ROOT, "oracle", "_ref", "refmath_cuda.so")
+    if os.path.exists(mpath):
+        spec = importlib.util.spec_from_file_location("refmath_cuda", mpath)
+        rmath = importlib.util.module_from_spec(spec)
+        spec.loader.exec_module(rmath)
+    gold_path = os.path.join(ROOT, "tests", "golden", "configs.json")
+    gold = json.load(open(gold_path)) if os.path.exists(gold_path) else {}
+    out = {}
+
+    def timed(fn, reps=3):
+        y = fn()
+        torch.cuda.synchronize()
+        return min(event_ms(fn) for _ in range(reps)), y
+
+    def sha(t):
+        return hashlib.sha256(t.cpu().numpy().tobytes()).hexdigest()
+
+    def same(a, b):
+        return bool(torch.equal(a.cpu().contiguous().view(torch.int32), b.cpu().contiguous().view(torch.int32)))
+
+    try:
+        # mm: config 1 and config 5
+        a, b = workloads.mm_square(1024, 0)
+        ad, bd = a.cuda(), b.cuda()
+        ms, y = timed(lambda: rc.mm(ad, bd, False, False))
+        out["mm 1024^3"] = {"ms": ms, "TFLOP/s": 2.0 * 1024 ** 3 / ms / 1e9,
+                            "equal_reference_cpu": sha(y) == gold.get("c1_mm_1024", {}).get("sha256")}
+        a, b = workloads.mm_large(16384, 4)
+        ad, bd = a.cuda(), b.cuda()
+        del a, b
+        ms, y = timed(lambda: rc.mm(ad, bd, False, False), reps=1)
+        g5 = os.path.join(ROOT, "tests", "golden", "mm16k.json")
+        out["mm 16384^3"] = {"ms": ms, "TFLOP/s": 2.0 * 16384 ** 3 / ms / 1e9,
+                             "equal_reference_cpu": os.path.exists(g5) and sha(y) == json.load(open(g5))["sha256"]}
+        del ad, bd, y
+        torch.cuda.empty_cache()
+        # the three convolutions at the shapes of config 4 (second layer: the expensive one)
+        g = torch.Generator().manual_seed(3)
+        x = torch.rand(256, 32, 26, 26, generator=g).cuda()
+        k = (torch.rand(64, 32, 3, 3, generator=g) - 0.5).cuda()
+        go = (torch.rand(256, 64, 24, 24, generator=g) - 0.5).cuda()
+        ms, y = timed(lambda: rc.conv2d(x, k, 1, 1, 0, 0, 1))
+        out["conv2d [256,32,26,26]*[64,32,3,3]"] = {"ms": ms, "equal_this_repo": same(y, ops.conv2d(x, k, (1, 1), (0, 0), 1))}
+        ms, y = timed(lambda: rc.conv2d_grad_input(go, k, 26, 26, 1, 1, 0, 0))
+        out["conv2d_grad_input"] = {"ms": ms, "equal_this_repo": same(y, ops.conv2d_grad_input((256, 32, 26, 26), k, go, (1, 1), (0, 0)))}
+        ms, y = timed(lambda: rc.conv2d_grad_kernel(go, x, 3, 3, 1, 1, 0, 0), reps=1)
+        out["conv2d_grad_kernel"] = {"ms": ms, "equal_this_repo": same(y, ops.conv2d_grad_kernel(x, (64, 32, 3, 3), go, (1, 1), (0, 0)))}
+        del x, k, go
+        # row sums of config 3
+        r = workloads.sum_rows(65536, 4096, 2).cuda()
+        ms, y = timed(lambda: rc.sum2d_dim1(r, False, False))
+        out["sum rows [65536,4096]"] = {"ms": ms, "GB/s": 4.0 * r.numel() / ms / 1e6,
+                                        "equal_reference_cpu": sha(y) == gold.get("c3_sum_rows_65536x4096", {}).get("sha256")}
+        # its one-chain sum: a single CTA walks the array, so only a short chain is timed (2^22 elements)
+        flat = r.view(-1)[:1 << 22].contiguous()
+        ms, y = timed(lambda: rc.sum1d(flat, False), reps=1)
+        out["sum1d chain [4194304]"] = {"ms": ms, "GB/s": 4.0 * flat.numel() / ms / 1e6,
+                                        "equal_this_repo": same(y, ops.sum1d(flat))}
+        del r, flat
+        torch.cuda.empty_cache()
+        if rmath is not None:
+            n = 1 << 28
+            xs = torch.cat(list(workloads.crmath_chunks(n, 1)))
+            xd, xad = xs.cuda(), xs.abs().cuda()
+            del xs
+            ms, y = timed(lambda: rmath.exp2d(xd.view(16384, 16384)))
+            out["exp(x) 2^28"] = {"ms": ms, "GB/s": 8.0 * n / ms / 1e6,
+                                  "equal_reference_cpu": sha(y) == gold.get("c2_crmath_2p28", {}).get("whole", {}).get("exp")}
+            ms, y = timed(lambda: rmath.log1d(xad))
+            out["log(|x|) 2^28"] = {"ms": ms, "GB/s": 8.0 * n / ms / 1e6,
+                                    "equal_reference_cpu": sha(y) == gold.get("c2_crmath_2p28", {}).get("whole", {}).get("log_abs")}
+            del xd, xad, y
+    except Exception as e:  # a report next to the measurement, never part of it
+        out["error"] = repr(e)[:300]
+    torch.cuda.empty_cache()
+    return out
 
 
 def extras_hbm(hbm_peak, peak_kind, n=1 << 28, which="all", steps=5, warmup=3):
@@ -398,8 +591,10 @@ def main():
     ap.add_argument("--size", type=int, default=16384, help="M = N = K of the headline product")
     ap.add_argument("--mode", default="auto", choices=["auto", "nccl", "p2p"])
     ap.add_argument("--ref-rows", type=int, default=16)
+    ap.add_argument("--ref-budget", type=float, default=100.0,
+                    help="seconds the reference arm may spend on its warm-up and timed steps")
     ap.add_argument("--cpu-budget", type=float, default=15.0)
-    ap.add_argument("--workload", default="mm", choices=["mm", "crmath", "sums", "cnn"],
+    ap.add_argument("--workload", default="mm", choices=["mm", "crmath", "sums", "cnn", "mmsmall", "refcuda", "chain"],
                     help="mm: the headline product; crmath / sums: only the HBM-bound kernels of "
                          "configs 2 / 3 at --elements; cnn: the config-4 training step "
                          "(these three are used for profiling captures)")
@@ -424,6 +619,15 @@ def main():
         if rank == 0:
             torch.cuda.set_device(local_rank)
             print(json.dumps(cnn_step_bench(args.steps, args.warmup)), flush=True)
+        return
+    if args.workload in ("mmsmall", "refcuda", "chain"):
+        if rank == 0:
+            torch.cuda.set_device(local_rank)
+            hbm_peak, peak_kind = measured_peaks()
+            res = (extras_mm(ffma_peak_tflops(False)) if args.workload == "mmsmall"
+                   else reference_cuda_bench() if args.workload == "refcuda"
+                   else extras_sum1d_full(hbm_peak, peak_kind, args.steps, args.warmup))
+            print(json.dumps({"workload": args.workload, "results": res}), flush=True)
         return
     if args.workload != "mm":
         if rank == 0:
@@ -497,7 +701,7 @@ def main():
         for _ in range(2):
             mm_from_host(sh, a_host, b_host, a_dev, b_dev, c_host)
         barrier()
-        ke = min(args.steps, 3)
+        ke = args.steps
         t0 = torch.cuda.Event(enable_timing=True)
         t1 = torch.cuda.Event(enable_timing=True)
         t0.record(cur)
@@ -556,7 +760,12 @@ def main():
             if not args.no_extra:
                 del a_dev, b_dev, sh
                 torch.cuda.empty_cache()
-                line["extra"] = extras_hbm(hbm_peak, peak_kind)
+                line["extra"] = extras_mm(peak)
+                line["extra"].update(extras_hbm(hbm_peak, peak_kind))
+                line["extra"]["sum1d chain [1073741824] (config 3)"] = extras_sum1d_full(hbm_peak, peak_kind)
+                ref_cuda = reference_cuda_bench()
+                if ref_cuda is not None:
+                    line["extra"]["reference CUDA backend (sm_100a build)"] = ref_cuda
                 # the callers' side of the path: one SGD step of the CNN workload on these operators
                 line["extra"]["cnn training step"] = cnn_step_bench(steps=5, warmup=3)
         print(json.dumps(line), flush=True)

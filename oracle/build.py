@@ -1,8 +1,8 @@
 """TEST INFRASTRUCTURE -- compiles oracle/repdl_oracle.c into oracle/librepdl_oracle.so.
 
-Usage: python oracle/build.py [--ref]   (--ref also runs oracle/build_ref.sh when the
-reference tree is present; that takes a few minutes because the reference's CUDA
-backend is compiled too).
+Usage: python oracle/build.py [--ref]   (--ref also runs oracle/build_ref.sh on the
+reference tree that the environment variable REPDL_REFERENCE names; that takes a few
+minutes because the reference's CUDA backend is compiled too).
 """
 import os
 import subprocess
@@ -28,8 +28,8 @@ def build_oracle(force=False):
 
 
 def build_ref():
-    ref = os.environ.get("REPDL_REFERENCE", "/root/reference")
-    if not os.path.isdir(ref):
+    ref = os.environ.get("REPDL_REFERENCE", "")
+    if not ref or not os.path.isdir(ref):
         return False
     subprocess.run(["bash", os.path.join(HERE, "build_ref.sh")], check=True)
     return True

@@ -12,14 +12,14 @@
 #   site/repdl/...                    the reference Python package
 #   site/repdl/backend/cpu*.so        reference CPU backend (backend/cpu/*.cpp)
 #   site/repdl/backend/cuda*.so       reference CUDA backend compiled for sm_100a
-#   refmath*.so                       12-line pybind shim exposing the reference's
+#   refmath.so, refmath_cuda.so       12-line pybind shims exposing the reference's
 #                                     exp2d/log1d (backend/cpu/math.cpp:19-47), which
 #                                     backend/cpu/bind.cpp:6-19 does not export
 set -euo pipefail
 HERE="$(cd "$(dirname "$0")" && pwd)"
-REF="${REPDL_REFERENCE:-/root/reference}"
+REF="${REPDL_REFERENCE:-}"
 OUT="$HERE/_ref"
-[ -d "$REF" ] || { echo "no reference tree at $REF; nothing to build"; exit 0; }
+[ -n "$REF" ] && [ -d "$REF" ] || { echo "REPDL_REFERENCE does not name a reference tree; nothing to build"; exit 0; }
 export CXX=/usr/bin/g++ CC=/usr/bin/gcc TORCH_CUDA_ARCH_LIST=10.0a MAX_JOBS="${MAX_JOBS:-8}"
 mkdir -p "$OUT"
 SCRATCH="$(mktemp -d /tmp/repdl_ref_build.XXXXXX)"

@@ -81,6 +81,8 @@ torch::Tensor conv2d(const torch::Tensor &input, const torch::Tensor &kernel, un
     torch::Tensor x = input.contiguous(), k = kernel.contiguous();
     const int64_t N = x.size(0), IC = x.size(1), H = x.size(2), W = x.size(3);
     const int64_t OC = k.size(0), KH = k.size(2), KW = k.size(3);
+    TORCH_CHECK(strideH > 0 && strideW > 0, "conv2d: stride must be positive");
+    TORCH_CHECK(H + 2 * paddingH >= KH && W + 2 * paddingW >= KW, "conv2d: the kernel does not fit into the padded image");
     const int64_t OH = (H + 2 * paddingH - KH) / strideH + 1, OW = (W + 2 * paddingW - KW) / strideW + 1;
     torch::Tensor out = torch::empty({N, OC, OH, OW}, input.options());
     ok(repdl_b200_conv2d(fp(x), fp(k), fpw(out), N, IC, H, W, OC, KH, KW, strideH, strideW,
@@ -99,6 +101,13 @@ torch::Tensor conv2d_grad_input(const torch::Tensor &grad_output, const torch::T
     c10::cuda::CUDAGuard guard(grad_output.device());
     torch::Tensor go = grad_output.contiguous(), k = kernel.contiguous();
     const int64_t N = go.size(0), OC = k.size(0), IC = k.size(1), KH = k.size(2), KW = k.size(3);
+    // the kernels index grad_output with the extents they derive from H, W: it must have them
+    TORCH_CHECK(strideH > 0 && strideW > 0, "conv2d_grad_input: stride must be positive");
+    TORCH_CHECK((int64_t)H + 2 * paddingH >= KH && (int64_t)W + 2 * paddingW >= KW,
+                "conv2d_grad_input: the kernel does not fit into the padded image");
+    TORCH_CHECK(go.size(1) == OC && go.size(2) == ((int64_t)H + 2 * paddingH - KH) / strideH + 1 &&
+                    go.size(3) == ((int64_t)W + 2 * paddingW - KW) / strideW + 1,
+                "conv2d_grad_input: grad_output does not have the shape of this convolution's output");
     torch::Tensor out = torch::empty({N, IC, (int64_t)H, (int64_t)W}, grad_output.options());
     ok(repdl_b200_conv2d_grad_input(fp(go), fp(k), fpw(out), N, IC, H, W, OC, KH, KW, strideH,
                                     strideW, paddingH, paddingW, cur_stream()),
@@ -116,6 +125,12 @@ torch::Tensor conv2d_grad_kernel(const torch::Tensor &grad_output, const torch::
     c10::cuda::CUDAGuard guard(input.device());
     torch::Tensor go = grad_output.contiguous(), x = input.contiguous();
     const int64_t N = x.size(0), IC = x.size(1), H = x.size(2), W = x.size(3), OC = go.size(1);
+    TORCH_CHECK(strideH > 0 && strideW > 0, "conv2d_grad_kernel: stride must be positive");
+    TORCH_CHECK(H + 2 * paddingH >= (int64_t)KH && W + 2 * paddingW >= (int64_t)KW,
+                "conv2d_grad_kernel: the kernel does not fit into the padded image");
+    TORCH_CHECK(go.size(0) == N && go.size(2) == (H + 2 * paddingH - (int64_t)KH) / strideH + 1 &&
+                    go.size(3) == (W + 2 * paddingW - (int64_t)KW) / strideW + 1,
+                "conv2d_grad_kernel: grad_output does not have the shape of this convolution's output");
     torch::Tensor out = torch::empty({OC, IC, (int64_t)KH, (int64_t)KW}, input.options());
     ok(repdl_b200_conv2d_grad_kernel(fp(go), fp(x), fpw(out), N, IC, H, W, OC, KH, KW, strideH,
                                      strideW, paddingH, paddingW, cur_stream()),

@@ -131,26 +131,45 @@ __global__ void __launch_bounds__(1024)
 predict_kernel(const double *__restrict__ node_sum, int nnodes, double *__restrict__ pred,
                double *__restrict__ rabs)
 {
+    // Thread t owns the consecutive nodes [t * per, (t + 1) * per) of every slab of 1024 * per
+    // nodes; a slab goes through shared memory so that global memory is read and written in order.
+    constexpr int PER = 4;
     __shared__ double wtot[32];
+    __shared__ double slab[1024 * PER + 1024 * PER / 32];  // padded: thread-consecutive reads without conflicts
+    __shared__ double carry_run, carry_var;
     const int t = threadIdx.x;
-    const int per = (nnodes + 1023) / 1024;
-    const int lo = min(t * per, nnodes), hi = min(lo + per, nnodes);
-    double s = 0.0;
-    for (int i = lo; i < hi; i++) s += node_sum[i];
-    double run = block_exclusive_scan_1024(s, wtot);
-    double v = 0.0;
-    for (int i = lo; i < hi; i++) {
-        pred[i] = run;
-        const double a = fabs(run);
-        run += node_sum[i];
-        const double dv = drift_variance(fmax(a, fabs(run)));
-        rabs[i] = dv;  // variance this node adds, replaced by the bound below
-        v += dv;
-    }
-    double var = block_exclusive_scan_1024(v, wtot);
-    for (int i = lo; i < hi; i++) {
-        var += rabs[i];
-        rabs[i] = DRIFT_SIGMAS * sqrt(var);
+    if (t == 0) carry_run = 0.0, carry_var = 0.0;
+    __syncthreads();
+    auto at = [](int i) { return i + (i >> 5); };
+    for (int base = 0; base < nnodes; base += 1024 * PER) {
+        const int count = min(1024 * PER, nnodes - base);
+        for (int i = t; i < 1024 * PER; i += 1024) slab[at(i)] = i < count ? node_sum[base + i] : 0.0;
+        __syncthreads();
+        double v[PER], s = 0.0;
+#pragma unroll
+        for (int k = 0; k < PER; k++) v[k] = slab[at(t * PER + k)], s += v[k];
+        double run = carry_run + block_exclusive_scan_1024(s, wtot);
+        double dv[PER], vs = 0.0;
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            const double a = fabs(run);
+            slab[at(t * PER + k)] = run;  // predicted state at the node's start
+            run += v[k];
+            dv[k] = drift_variance(fmax(a, fabs(run)));
+            vs += dv[k];
+        }
+        __syncthreads();
+        for (int i = t; i < count; i += 1024) pred[base + i] = slab[at(i)];
+        double var = carry_var + block_exclusive_scan_1024(vs, wtot);  // (syncs: the slab is free again)
+#pragma unroll
+        for (int k = 0; k < PER; k++) {
+            var += dv[k];
+            slab[at(t * PER + k)] = DRIFT_SIGMAS * sqrt(var);
+        }
+        __syncthreads();
+        for (int i = t; i < count; i += 1024) rabs[base + i] = slab[at(i)];
+        if (t == 1023) carry_run = run, carry_var = var;
+        __syncthreads();
     }
 }
 
@@ -227,10 +246,14 @@ __device__ __forceinline__ void classify_node_leaves(const float *__restrict__ x
     for (int t = warp; t < TILES_PER_NODE; t += NW) {
         float v[LEAF];
         load_tile_leaves(x, n, node * NODE + (int64_t)t * TILE, vec, my, v);
-        double ls = 0.0;
+        // the leaf's sum, for the prediction only: an fp32 tree (its error is far below the drift
+        // bound; fp64 conversions and additions per element would cost half as much as the summary)
+        float t8[8];
 #pragma unroll
-        for (int i = 0; i < LEAF; i += 4)
-            ls += ((double)v[i] + (double)v[i + 1]) + ((double)v[i + 2] + (double)v[i + 3]);
+        for (int i = 0; i < 8; i++)
+            t8[i] = __fadd_rn(__fadd_rn(v[4 * i], v[4 * i + 1]), __fadd_rn(v[4 * i + 2], v[4 * i + 3]));
+        const double ls = (double)__fadd_rn(__fadd_rn(__fadd_rn(t8[0], t8[1]), __fadd_rn(t8[2], t8[3])),
+                                            __fadd_rn(__fadd_rn(t8[4], t8[5]), __fadd_rn(t8[6], t8[7])));
         double incl = ls;
 #pragma unroll
         for (int d = 1; d < 32; d <<= 1) {
@@ -445,46 +468,49 @@ constexpr int EMIT_WARPS = 4;
 __global__ void __launch_bounds__(EMIT_WARPS * 32)
 emit_kernel(const float *__restrict__ x, int64_t n, const double *__restrict__ tile_sum,
             const double *__restrict__ pred, const double *__restrict__ rabs,
-            const NodeRec *__restrict__ rec, Item *__restrict__ items, Header *__restrict__ hdr, int vec)
+            const NodeRec *__restrict__ rec, Item *__restrict__ items, Header *__restrict__ hdr, int vec,
+            int64_t nnodes)
 {
     __shared__ __align__(16) float tbuf[EMIT_WARPS * 32 * RUN_PITCH];
     __shared__ double tpre[TILES_PER_NODE];
     __shared__ unsigned short code[LEAVES_PER_NODE];
     __shared__ Summ summ[LEAVES_PER_NODE];
     __shared__ int wtot[EMIT_WARPS];
-    const int64_t node = blockIdx.x;
-    const NodeRec r = rec[node];
-    Item *out = items + r.off;
-    const int leaf0 = (int)(node * LEAVES_PER_NODE);
-    if (r.kind != N_MIXED) {
-        if (threadIdx.x == 0)
-            out[0] = r.kind == N_SMOOTH ? make_item(K_RUN, r.pos, r.sek, 0, leaf0, LEAVES_PER_NODE)
-                                        : make_item(K_RAWSPAN, summ_invalid(), 0, 0, leaf0, LEAVES_PER_NODE);
-        return;
-    }
-    classify_node_leaves<EMIT_WARPS, true>(x, n, node, vec != 0, tile_sum, pred[node], rabs[node], tbuf, tpre,
-                                           code, summ, nullptr);
-    // thread t owns the consecutive leaves [t * PER, (t + 1) * PER)
     constexpr int PER = LEAVES_PER_NODE / (EMIT_WARPS * 32);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int first = threadIdx.x * PER;
-    int mine = 0;
-    for (int k = 0; k < PER; k++) mine += leaf_item_count(code, first + k);
-    int incl = mine;
+    for (int64_t node = blockIdx.x; node < nnodes; node += gridDim.x) {
+        const NodeRec r = rec[node];
+        Item *out = items + r.off;
+        const int leaf0 = (int)(node * LEAVES_PER_NODE);
+        if (r.kind != N_MIXED) {
+            if (threadIdx.x == 0)
+                out[0] = r.kind == N_SMOOTH ? make_item(K_RUN, r.pos, r.sek, 0, leaf0, LEAVES_PER_NODE)
+                                            : make_item(K_RAWSPAN, summ_invalid(), 0, 0, leaf0, LEAVES_PER_NODE);
+            continue;
+        }
+        classify_node_leaves<EMIT_WARPS, true>(x, n, node, vec != 0, tile_sum, pred[node], rabs[node], tbuf,
+                                               tpre, code, summ, nullptr);
+        // thread t owns the consecutive leaves [t * PER, (t + 1) * PER)
+        const int first = threadIdx.x * PER;
+        int mine = 0;
+        for (int k = 0; k < PER; k++) mine += leaf_item_count(code, first + k);
+        int incl = mine;
 #pragma unroll
-    for (int d = 1; d < 32; d <<= 1) {
-        const int up = __shfl_up_sync(0xffffffffu, incl, d);
-        if (lane >= d) incl += up;
+        for (int d = 1; d < 32; d <<= 1) {
+            const int up = __shfl_up_sync(0xffffffffu, incl, d);
+            if (lane >= d) incl += up;
+        }
+        if (lane == 31) wtot[warp] = incl;
+        __syncthreads();
+        int idx = incl - mine;
+        for (int w = 0; w < warp; w++) idx += wtot[w];
+        for (int k = 0; k < PER; k++) {
+            leaf_emit_items(code, summ, first + k, leaf0, out + idx);
+            idx += leaf_item_count(code, first + k);
+        }
+        if (threadIdx.x == EMIT_WARPS * 32 - 1 && idx != r.count) hdr->error = 1;
+        __syncthreads();  // the shared arrays are reused by the next node
     }
-    if (lane == 31) wtot[warp] = incl;
-    __syncthreads();
-    int idx = incl - mine;
-    for (int w = 0; w < warp; w++) idx += wtot[w];
-    for (int k = 0; k < PER; k++) {
-        leaf_emit_items(code, summ, first + k, leaf0, out + idx);
-        idx += leaf_item_count(code, first + k);
-    }
-    if (threadIdx.x == EMIT_WARPS * 32 - 1 && idx != r.count) hdr->error = 1;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -780,7 +806,8 @@ static int sum1d_long(const float *x, float *out, int64_t n, float factor, char 
     if ((e = launch_status())) return e;
     plan_kernel<<<1, 1024, 0, st>>>(rec, (int)nn, L.cap, hdr, items);
     if ((e = launch_status())) return e;
-    emit_kernel<<<nn, EMIT_WARPS * 32, 0, st>>>(x, n, tile_sum, pred, rabs, rec, items, hdr, vec);
+    const unsigned emit_grid = nn;  // one node per CTA (smooth nodes: one item each, written by thread 0)
+    emit_kernel<<<emit_grid, EMIT_WARPS * 32, 0, st>>>(x, n, tile_sum, pred, rabs, rec, items, hdr, vec, L.nnodes);
     if ((e = launch_status())) return e;
     walk_kernel<<<1, WALK_THREADS, WALK_SMEM_BYTES, st>>>(x, n, hdr, items, factor, out);
     return launch_status();

@@ -1,4 +1,4 @@
-"""Row-sharded matrix multiplication across the GPUs of one node.
+"""Row-sharded matrix multiplication (and batch-sharded convolution) across the GPUs of one node.
 
 microsoft/RepDL has no multi-GPU code; this is the one distributed strategy the operator backend
 needs: A is partitioned by rows, B is replicated, every rank computes its own row panel of C with
@@ -12,6 +12,13 @@ the panels are gathered so that every rank ends with the full C.
   * "nccl": torch.distributed all_gather_into_tensor (NCCL over NVLink) written in place into the
             full C after the local panel is done -- the baseline.
 "auto" tries "p2p" and falls back to "nccl" when symmetric memory cannot be set up.
+
+Lifetime of the result.  `ShardedMM` returns its own buffer C, the same one on every call.  In
+"p2p" mode the OTHER ranks write into it, so each call begins with a small all-reduce that no
+rank's stream passes before every rank's stream has reached it: whatever a rank queued on its
+stream to read the previous result (before making this call) has finished by the time any peer
+starts to overwrite it.  Work on other streams, or on the host after the call returns, must be
+ordered by the caller, as with any buffer that the next call reuses.
 
 The panel product itself is injectable (`mm_into`), which lets the partitioning and gathering logic
 be exercised on CPU ranks over gloo with any reference implementation of the product.
@@ -83,6 +90,9 @@ class ShardedMM:
 
     def _p2p(self, a_panel, b):
         from ._cabi import check, lib
+        # no peer may start storing into this rank's C before this rank has finished with the
+        # previous result: nothing passes this collective until every rank's stream has reached it
+        dist.all_reduce(self._flag, group=self.group)
         st = torch.cuda.current_stream(self.device).cuda_stream
         check(lib.repdl_b200_mm_allgather(a_panel.data_ptr(), b.data_ptr(), self._peer_ptrs,
                                           self.world, self.row0, self.Mp, self.N, self.K, 0, 0,
@@ -104,6 +114,59 @@ class ShardedMM:
         if self.world > 1:
             dist.all_gather_into_tensor(self.C, self.my_rows(), group=self.group)
         return self.C
+
+
+class ShardedConv2d:
+    """conv2d with the batch partitioned over the ranks (images are independent chains, microsoft/RepDL
+    backend/cpu/convolution.cpp:24, so the bits are those of a one-GPU run): every rank convolves its
+    N/world images with the replicated kernel and the outputs are all-gathered in place (NCHW is
+    batch-major, so a rank's images are one contiguous block of the result).
+
+    `conv_into(x_part, kernel, out_part)` is injectable like ShardedMM's product, which lets the
+    partitioning be exercised on CPU ranks over gloo."""
+
+    def __init__(self, input_shape, kernel_shape, stride=(1, 1), padding=(0, 0), groups=1, group=None,
+                 device=None, conv_into=None):
+        self.group = group
+        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
+        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        N, IC, H, W = input_shape
+        OC, _, KH, KW = kernel_shape
+        if N % self.world:
+            raise ValueError("batch (%d) must be divisible by the number of ranks (%d)" % (N, self.world))
+        self.stride, self.padding, self.groups = tuple(stride), tuple(padding), groups
+        OH = (H + 2 * self.padding[0] - KH) // self.stride[0] + 1
+        OW = (W + 2 * self.padding[1] - KW) // self.stride[1] + 1
+        if OH <= 0 or OW <= 0:
+            raise ValueError("the kernel does not fit into the padded image")
+        self.Np = N // self.world
+        if device is None:
+            device = torch.device("cuda", torch.cuda.current_device())
+        self.out = torch.empty((N, OC, OH, OW), dtype=torch.float32, device=device)
+        self.conv_into = conv_into or self._ops_conv_into
+        self.kernel_launches = 0
+
+    def _ops_conv_into(self, x_part, kernel, out_part):
+        from . import ops
+        out_part.copy_(ops.conv2d(x_part, kernel, self.stride, self.padding, self.groups))
+
+    @property
+    def n0(self):
+        return self.rank * self.Np
+
+    def my_images(self):
+        return self.out[self.n0:self.n0 + self.Np]
+
+    def __call__(self, x_part, kernel):
+        """x_part: this rank's [N/world, IC, H, W] images; kernel: [OC, IC/groups, KH, KW].  Returns
+        the full [N, OC, OH, OW] output on every rank."""
+        if x_part.shape[0] != self.Np:
+            raise ValueError("expected %d images per rank, got %d" % (self.Np, x_part.shape[0]))
+        self.conv_into(x_part, kernel, self.my_images())
+        self.kernel_launches += 1
+        if self.world > 1:
+            dist.all_gather_into_tensor(self.out, self.my_images(), group=self.group)
+        return self.out
 
 
 _copy_streams = {}
@@ -128,12 +191,28 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chun
 
     Several GPUs: every rank has the same B in host memory, so each uploads only its 1/world of B's
     rows and the ranks all-gather B over NVLink -- world times less PCIe traffic for B than uploading
-    it everywhere -- before the sharded product; the C panel comes back at the end.
+    it everywhere.  The slice of B goes first on a copy stream and the A panel behind it, so that A
+    arrives while B is being gathered; then the sharded product, and the C panel comes back.
     """
     dev = a_dev.device
     if sharded.world > 1:
         kp = b_dev.shape[0] // sharded.world
-        if b_dev.shape[0] % sharded.world == 0 and b_dev.is_contiguous():
+        if dev.type == "cuda" and b_dev.shape[0] % sharded.world == 0 and b_dev.is_contiguous():
+            lo = sharded.rank * kp
+            cur = torch.cuda.current_stream(dev)
+            up, _ = _side_streams(dev)
+            up.wait_stream(cur)  # the buffers may still be in use by what the caller queued before
+            with torch.cuda.stream(up):
+                b_dev[lo:lo + kp].copy_(b_host[lo:lo + kp], non_blocking=True)
+                b_there = torch.cuda.Event()
+                b_there.record(up)
+                a_dev.copy_(a_host_panel, non_blocking=True)
+                a_there = torch.cuda.Event()
+                a_there.record(up)
+            cur.wait_event(b_there)
+            dist.all_gather_into_tensor(b_dev, b_dev[lo:lo + kp], group=sharded.group)
+            cur.wait_event(a_there)
+        elif b_dev.shape[0] % sharded.world == 0 and b_dev.is_contiguous():
             lo = sharded.rank * kp
             a_dev.copy_(a_host_panel, non_blocking=True)
             b_dev[lo:lo + kp].copy_(b_host[lo:lo + kp], non_blocking=True)

@@ -51,6 +51,14 @@ def mm(input: torch.Tensor, mat2: torch.Tensor, transA: bool = False,
     return out
 
 
+def _out_extent(size, pad, k, stride, what):
+    if stride <= 0:
+        raise ValueError(what + ": stride must be positive")
+    if size + 2 * pad < k:
+        raise ValueError(what + ": the kernel does not fit into the padded image")
+    return (size + 2 * pad - k) // stride + 1
+
+
 def conv2d(input, weight, stride, padding, groups) -> torch.Tensor:
     _need(input, "input", 4), _need(weight, "weight", 4)
     x, k = input.contiguous(), weight.contiguous()
@@ -58,8 +66,8 @@ def conv2d(input, weight, stride, padding, groups) -> torch.Tensor:
     OC, ICg, KH, KW = k.shape
     if ICg * groups != IC:
         raise ValueError("conv2d: weight.shape[1] * groups != input channels")
-    OH = (H + 2 * padding[0] - KH) // stride[0] + 1
-    OW = (W + 2 * padding[1] - KW) // stride[1] + 1
+    OH = _out_extent(H, padding[0], KH, stride[0], "conv2d")
+    OW = _out_extent(W, padding[1], KW, stride[1], "conv2d")
     out = torch.empty((N, OC, OH, OW), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         check(lib.repdl_b200_conv2d(x.data_ptr(), k.data_ptr(), out.data_ptr(), N, IC, H, W, OC, KH,
@@ -74,6 +82,12 @@ def conv2d_grad_input(input_shape, weight, grad_output, stride, padding) -> torc
     OC, IC, KH, KW = k.shape
     N = go.shape[0]
     H, W = int(input_shape[2]), int(input_shape[3])
+    # the kernels index grad_output with the extents they derive from H and W: it must have them
+    want = (N, OC, _out_extent(H, padding[0], KH, stride[0], "conv2d_grad_input"),
+            _out_extent(W, padding[1], KW, stride[1], "conv2d_grad_input"))
+    if tuple(go.shape) != want:
+        raise ValueError("conv2d_grad_input: grad_output has shape %s, this convolution's output has %s"
+                         % (tuple(go.shape), want))
     out = torch.empty((N, IC, H, W), dtype=torch.float32, device=go.device)
     with torch.cuda.device(go.device):
         check(lib.repdl_b200_conv2d_grad_input(go.data_ptr(), k.data_ptr(), out.data_ptr(), N, IC, H,
@@ -82,12 +96,22 @@ def conv2d_grad_input(input_shape, weight, grad_output, stride, padding) -> torc
     return out
 
 
+def _check_grad_output(go, N, OC, H, W, KH, KW, stride, padding, what, weight_shape=None):
+    if weight_shape is not None and (int(weight_shape[0]) != OC):
+        raise ValueError("%s: grad_output has %d channels, the kernel %d" % (what, OC, int(weight_shape[0])))
+    want = (N, OC, _out_extent(H, padding[0], KH, stride[0], what), _out_extent(W, padding[1], KW, stride[1], what))
+    if tuple(go.shape) != want:
+        raise ValueError("%s: grad_output has shape %s, this convolution's output has %s"
+                         % (what, tuple(go.shape), want))
+
+
 def conv2d_grad_kernel(input, weight_shape, grad_output, stride, padding) -> torch.Tensor:
     _need(input, "input", 4), _need(grad_output, "grad_output", 4)
     x, go = input.contiguous(), grad_output.contiguous()
     N, IC, H, W = x.shape
     OC = go.shape[1]
     KH, KW = int(weight_shape[2]), int(weight_shape[3])
+    _check_grad_output(go, N, OC, H, W, KH, KW, stride, padding, "conv2d_grad_kernel", weight_shape)
     out = torch.empty((OC, IC, KH, KW), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):
         check(lib.repdl_b200_conv2d_grad_kernel(go.data_ptr(), x.data_ptr(), out.data_ptr(), N, IC,
@@ -104,6 +128,7 @@ def conv2d_grad_kernel_bias(input, weight_shape, grad_output, stride, padding):
     N, IC, H, W = x.shape
     OC = go.shape[1]
     KH, KW = int(weight_shape[2]), int(weight_shape[3])
+    _check_grad_output(go, N, OC, H, W, KH, KW, stride, padding, "conv2d_grad_kernel_bias", weight_shape)
     gw = torch.empty((OC, IC, KH, KW), dtype=torch.float32, device=x.device)
     gb = torch.empty((OC,), dtype=torch.float32, device=x.device)
     with torch.cuda.device(x.device):

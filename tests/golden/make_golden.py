@@ -8,12 +8,13 @@ machines that do not have the reference.
     python tests/golden/make_golden.py configs    # tests/golden/configs.json       (~15 min)
     python tests/golden/make_golden.py cnn        # tests/golden/cnn_steps.json     (~10 min)
     python tests/golden/make_golden.py mm16k      # tests/golden/mm16k.json         (~10 min)
+    python tests/golden/make_golden.py mm16k_reference   # the same file from the reference alone (~35 min)
     python tests/golden/make_golden.py optim      # tests/golden/optim_steps.json   (seconds)
 
 Every value is produced by the reference's own CPU backend (repdl.backend.cpu, plus the exp2d /
-log1d shim and repdl/ops.py's ATen div / sqrt), except the full 16384^3 product, whose hash comes
-from the C oracle after 512 of its rows have been compared bit for bit with the reference's
-transB path (a full reference run takes over an hour on 8 cores).
+log1d shim and repdl/ops.py's ATen div / sqrt).  The full 16384^3 product is first hashed from the
+C oracle (`mm16k`, with 512 rows compared with the reference) and then recomputed entirely by the
+reference's transB path (`mm16k_reference`), which replaces the hashes by the reference's own.
 """
 import hashlib
 import json
@@ -156,6 +157,38 @@ def mm16k(ref):
     dump("mm16k.json", out)
 
 
+def mm16k_reference(ref):
+    """Config 5 computed ENTIRELY by the reference's CPU backend (its transB path on a pre-transposed
+    B: the same chains as the plain layout, backend/cpu/matrix_multiplication.cpp:29-31, at a
+    cache-friendly stride), in row blocks, about half an hour on 8 cores.  Replaces the hashes of
+    mm16k.json by the reference's own and records that they equal the C oracle's."""
+    import hashlib
+    path = os.path.join(HERE, "mm16k.json")
+    out = json.load(open(path))
+    a, b = workloads.mm_large(16384, 4)
+    assert [sha(a), sha(b)] == out["input_sha256"]
+    bt = b.t().contiguous()
+    whole, blocks = hashlib.sha256(), []
+    t = time.time()
+    for r0 in range(0, 16384, 2048):
+        blk = hashlib.sha256()
+        for s0 in range(r0, r0 + 2048, 256):
+            c = ref.cpu.mm(a[s0:s0 + 256].contiguous(), bt, False, True)
+            raw = c.numpy().tobytes()
+            whole.update(raw)
+            blk.update(raw)
+        blocks.append(blk.hexdigest())
+        print("mm16k reference rows", r0 + 2048, "%.0fs" % (time.time() - t), flush=True)
+    out["reference_full_seconds"] = time.time() - t
+    out["reference_rows_checked"] = 16384
+    out["reference_rows_equal"] = whole.hexdigest() == out["sha256"] and blocks == out["row_block_2048_sha256"]
+    out["sha256_source"] = "reference CPU backend, whole product; equal to the C oracle's"
+    assert out["reference_rows_equal"], (whole.hexdigest(), out["sha256"])
+    out["sha256"], out["row_block_2048_sha256"] = whole.hexdigest(), blocks
+    out.pop("reference_rows_seconds", None)
+    dump("mm16k.json", out)
+
+
 def optim(ref):
     """Parameter hashes after each of six steps of the reference's own Adam (repdl/optim.py) on CPU
     tensors, for four settings; and of the two-rounding SGD update written with torch's CPU ops."""
@@ -186,4 +219,5 @@ if __name__ == "__main__":
         sys.exit("oracle/_ref is not built (run oracle/build_ref.sh where the reference is mounted)")
     what = sys.argv[1:] or ["small"]
     for w in what:
-        {"small": small, "configs": configs, "cnn": cnn, "mm16k": mm16k, "optim": optim}[w](ref)
+        {"small": small, "configs": configs, "cnn": cnn, "mm16k": mm16k, "mm16k_reference": mm16k_reference,
+         "optim": optim}[w](ref)

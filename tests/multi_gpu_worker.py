@@ -25,15 +25,21 @@ def main():
     a = (torch.rand(M, K, generator=g) * 2 - 1).to(dev)
     b = (torch.rand(K, N, generator=g) * 2 - 1).to(dev)
     alone = ops.mm(a, b)
+    # a second pair of operands: consecutive calls reuse the result buffer with DIFFERENT contents,
+    # and the previous result is read on the stream right up to the next call (no barrier here:
+    # ordering the peers' stores against that read is the product's job)
+    a2 = (torch.rand(M, K, generator=g) * 2 - 1).to(dev)
+    alone2 = ops.mm(a2, b)
     out = {"rank": rank}
     for mode in ("nccl", "auto"):
         sh = ShardedMM(M, N, K, device=dev, mode=mode)
-        for rep in range(2):
-            sh.C.zero_()
-            dist.barrier()
-            c = sh(a[sh.row0:sh.row0 + sh.Mp].contiguous(), b)
-            torch.cuda.synchronize()
-            out["%s_%d" % (mode, rep)] = bool(torch.equal(c, alone))
+        flags = []
+        for rep in range(6):
+            src, want = (a, alone) if rep % 2 == 0 else (a2, alone2)
+            c = sh(src[sh.row0:sh.row0 + sh.Mp].contiguous(), b)
+            flags.append((c == want).all())  # queued on the stream; the next call follows at once
+        torch.cuda.synchronize()
+        out["%s_0" % mode] = out["%s_1" % mode] = all(bool(f) for f in flags)
         out[mode + "_mode"] = sh.mode
         if hasattr(sh, "p2p_error"):
             out["p2p_error"] = sh.p2p_error

@@ -30,3 +30,6 @@ def test_row_sharded_mm_matches_single_gpu():
     for r in ranks:
         for key in ("nccl_0", "nccl_1", "auto_0", "auto_1", "from_host"):
             assert r[key], (r, key)
+        # the GPUs of one B200 node reach each other's memory: "auto" must really have taken the
+        # epilogue-store path, not quietly fallen back to NCCL
+        assert r["auto_mode"] == "p2p", r

@@ -163,6 +163,27 @@ def test_scalar_division_with_subnormal_quotients(ops):
     assert ops.div(x.cuda(), 98.0).cpu().view(torch.int32).item() == 2
 
 
+def test_conv_backward_rejects_inconsistent_shapes(ops):
+    """The backward kernels index grad_output with extents derived from H, W / KH, KW: a grad_output
+    of any other shape is refused on the host instead of being read out of bounds."""
+    x = torch.zeros(2, 3, 8, 8, device="cuda")
+    k = torch.zeros(4, 3, 3, 3, device="cuda")
+    good = torch.zeros(2, 4, 6, 6, device="cuda")
+    ops.conv2d_grad_input(x.shape, k, good, (1, 1), (0, 0))
+    ops.conv2d_grad_kernel(x, k.shape, good, (1, 1), (0, 0))
+    for bad in (torch.zeros(2, 4, 7, 6, device="cuda"), torch.zeros(2, 5, 6, 6, device="cuda")):
+        with pytest.raises(ValueError):
+            ops.conv2d_grad_input(x.shape, k, bad, (1, 1), (0, 0))
+        with pytest.raises(ValueError):
+            ops.conv2d_grad_kernel(x, k.shape, bad, (1, 1), (0, 0))
+    with pytest.raises(ValueError):
+        ops.conv2d_grad_kernel(x, k.shape, torch.zeros(3, 4, 6, 6, device="cuda"), (1, 1), (0, 0))
+    with pytest.raises(ValueError):
+        ops.conv2d(x, torch.zeros(4, 3, 9, 9, device="cuda"), (1, 1), (0, 0), 1)  # kernel larger than the image
+    with pytest.raises(ValueError):
+        ops.conv2d(x, k, (0, 1), (0, 0), 1)
+
+
 def test_mm_from_host_pipeline_equals_one_launch(ops):
     """The pipelined host-operand step (row blocks uploaded, multiplied and downloaded on three
     streams) gives the bits of the one-launch product, twice in a row on the same buffers."""
