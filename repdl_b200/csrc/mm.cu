@@ -16,43 +16,26 @@
 // product is -0, and acc + (-0) == acc for EVERY acc including -0, +0, inf and NaN, so the padded
 // steps are exact identities (a +0 pad would turn an accumulator of -0 into +0).
 //
-// The inner product runs on Blackwell's packed FP32 FMA, fma.rn.f32x2: one instruction performs two
-// independent IEEE single-rounding FMAs on a 64-bit register pair -- the same bits as two scalar
-// FFMAs, in half the issue slots, which leaves room for the shared-memory loads without starving
-// the FMA pipe.  Accumulators live as (j, j+1) column pairs; the B fragment arrives as pairs from
-// LDS.128; the A slab is stored in shared memory with every value DUPLICATED, so that the (a, a)
-// broadcast pair also arrives straight from LDS.128 with no register moves.
+// (Blackwell's packed fma.rn.f32x2 gives the same bits in half the issue slots, but measured slower
+// here -- 36-44 against 53 TFLOP/s -- because its operand pairs cost register moves or a duplicated
+// shared-memory operand; the scalar FFMA loop below is what ships.)
 #include "common.cuh"
 
 namespace repdl_b200 {
 namespace {
 
-#ifndef REPDL_MM_BK
-#define REPDL_MM_BK 16
-#endif
-#ifndef REPDL_MM_MINB_BIG
-#define REPDL_MM_MINB_BIG 1
-#endif
-#ifndef REPDL_MM_KUNROLL
-#define REPDL_MM_KUNROLL REPDL_MM_BK  // k-steps of a slab unrolled back to back
-#endif
-#ifndef REPDL_MM_GROUP
-#define REPDL_MM_GROUP 8
-#endif
-#define REPDL_PRAGMA(x) _Pragma(#x)
-#define REPDL_UNROLL(n) REPDL_PRAGMA(unroll n)
-constexpr int BK = REPDL_MM_BK;
+constexpr int BK = 16;  // k-steps per slab, unrolled back to back
+
 
 // Cooperative loader for one operand slab of BX (rows or columns of C) x BK (k).
 //   KCONTIG = true : element (x, k) lives at X[x * ld + k]   (A of a plain mm, B of transB)
 //   KCONTIG = false: element (x, k) lives at X[k * ld + x]   (B of a plain mm, A of transA)
 //   VEC            : 128-bit global loads (caller guarantees 16 B alignment of every group)
-//   DUP            : every value is written twice, S[k][2x] = S[k][2x+1] (the A operand)
-// Shared layout is always S[k][x] (S[k][2x], S[k][2x+1] when DUP) with a padded row pitch.
-template <int BX, int NT, bool KCONTIG, bool VEC, bool DUP>
+// Shared layout is always S[k][x] with a padded row pitch.
+template <int BX, int NT, bool KCONTIG, bool VEC>
 struct SlabLoader {
     static constexpr int NV = BX * BK / 4 / NT;
-    static constexpr int PITCH = (DUP ? 2 * BX : BX) + 4;
+    static constexpr int PITCH = BX + 4;
     float4 v[NV];
 
     __device__ __forceinline__ void load(const float *__restrict__ X, int64_t ld, int x0, int k0,
@@ -99,28 +82,14 @@ struct SlabLoader {
             if (KCONTIG) {
                 int x = idx / (BK / 4);
                 int k = (idx % (BK / 4)) * 4;
-                if (DUP) {
-                    *reinterpret_cast<float2 *>(&S[k + 0][2 * x]) = make_float2(v[i].x, v[i].x);
-                    *reinterpret_cast<float2 *>(&S[k + 1][2 * x]) = make_float2(v[i].y, v[i].y);
-                    *reinterpret_cast<float2 *>(&S[k + 2][2 * x]) = make_float2(v[i].z, v[i].z);
-                    *reinterpret_cast<float2 *>(&S[k + 3][2 * x]) = make_float2(v[i].w, v[i].w);
-                } else {
-                    S[k + 0][x] = v[i].x;
-                    S[k + 1][x] = v[i].y;
-                    S[k + 2][x] = v[i].z;
-                    S[k + 3][x] = v[i].w;
-                }
+                S[k + 0][x] = v[i].x;
+                S[k + 1][x] = v[i].y;
+                S[k + 2][x] = v[i].z;
+                S[k + 3][x] = v[i].w;
             } else {
                 int k = idx / (BX / 4);
                 int x = (idx % (BX / 4)) * 4;
-                if (DUP) {
-                    *reinterpret_cast<float4 *>(&S[k][2 * x]) =
-                        make_float4(v[i].x, v[i].x, v[i].y, v[i].y);
-                    *reinterpret_cast<float4 *>(&S[k][2 * x + 4]) =
-                        make_float4(v[i].z, v[i].z, v[i].w, v[i].w);
-                } else {
-                    *reinterpret_cast<float4 *>(&S[k][x]) = v[i];
-                }
+                *reinterpret_cast<float4 *>(&S[k][x]) = v[i];
             }
         }
     }
@@ -130,7 +99,7 @@ struct SlabLoader {
 // tiles are visited in groups of GROUP tile-rows, column by column inside a group.
 __device__ __forceinline__ void tile_of_cta(int pid, int tilesM, int tilesN, int &tm, int &tn)
 {
-    constexpr int GROUP = REPDL_MM_GROUP;
+    constexpr int GROUP = 8;
     int per_group = GROUP * tilesN;
     int g = pid / per_group;
     int first = g * GROUP;
@@ -153,14 +122,6 @@ struct OutSet {
 // sitting q * (tile extent / quads) apart, so that the 8 lanes of a warp that differ in their
 // column read 8 consecutive 16-byte groups of a shared-memory row (no bank conflicts) and lanes that
 // share a row or a column get their fragment by broadcast.
-#ifndef REPDL_MM_F2
-#define REPDL_MM_F2 0   // 1: inner product on the packed fma.rn.f32x2 (same bits; measured slower)
-#endif
-#ifndef REPDL_MM_ORDER
-#define REPDL_MM_ORDER 0
-#endif
-constexpr bool kF2 = REPDL_MM_F2 != 0;
-
 template <int BM, int BN, int TM, int TN, bool A_KC, bool B_KC, bool VEC, int MINB, int D>
 __global__ void __launch_bounds__((BM / TM) * (BN / TN), MINB)
 sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const OutSet out, int M,
@@ -169,8 +130,8 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
     constexpr int NT = (BM / TM) * (BN / TN);
     constexpr int QM = TM / 4, QN = TN / 4;
     constexpr int WX = (BN / TN) / 8;  // warps along n; a warp is 8 lanes along n x 4 along m
-    using LoadA = SlabLoader<BM, NT, A_KC, VEC, kF2>;
-    using LoadB = SlabLoader<BN, NT, B_KC, VEC, false>;
+    using LoadA = SlabLoader<BM, NT, A_KC, VEC>;
+    using LoadB = SlabLoader<BN, NT, B_KC, VEC>;
     constexpr int PA = LoadA::PITCH, PB = LoadB::PITCH;
     extern __shared__ __align__(16) float smem[];
     float(*As)[BK][PA] = reinterpret_cast<float(*)[BK][PA]>(smem);
@@ -184,14 +145,11 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
     const int tx = (wid % WX) * 8 + (lane & 7);
     const int ty = (wid / WX) * 4 + (lane >> 3);
 
-    float acc[TM][TN];                   // scalar mode
-    unsigned long long acc2[TM][TN / 2];  // packed mode: columns (2p, 2p+1) of row i
+    float acc[TM][TN];
 #pragma unroll
     for (int i = 0; i < TM; i++) {
 #pragma unroll
         for (int j = 0; j < TN; j++) acc[i][j] = 0.0f;
-#pragma unroll
-        for (int j = 0; j < TN / 2; j++) acc2[i][j] = 0ull;  // (+0.0f, +0.0f)
     }
 
     // D register sets hold the slabs kt + 1 .. kt + D on their way from global to shared memory.
@@ -223,52 +181,23 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
             la[s].load(A, lda, m0, (kt + D) * BK, M, K, -0.0f, t);
             lb[s].load(B, ldb, n0, (kt + D) * BK, N, K, 0.0f, t);
         }
-        REPDL_UNROLL(REPDL_MM_KUNROLL)
+#pragma unroll
         for (int k = 0; k < BK; k++) {
-            if constexpr (kF2) {
-                unsigned long long a[TM], b[TN / 2];  // a[i] = (a_i, a_i); b[p] = (b_2p, b_2p+1)
+            float a[TM], b[TN];
 #pragma unroll
-                for (int q = 0; q < QM; q++) {
-                    const float *src = &As[cur][k][2 * (q * (BM / QM) + ty * 4)];
-                    ulonglong2 v0 = *reinterpret_cast<const ulonglong2 *>(src);
-                    ulonglong2 v1 = *reinterpret_cast<const ulonglong2 *>(src + 4);
-                    a[q * 4 + 0] = v0.x, a[q * 4 + 1] = v0.y, a[q * 4 + 2] = v1.x, a[q * 4 + 3] = v1.y;
-                }
-#pragma unroll
-                for (int q = 0; q < QN; q++) {
-                    ulonglong2 v =
-                        *reinterpret_cast<const ulonglong2 *>(&Bs[cur][k][q * (BN / QN) + tx * 4]);
-                    b[q * 2 + 0] = v.x, b[q * 2 + 1] = v.y;
-                }
-#pragma unroll
-                for (int i = 0; i < TM; i++)
-#pragma unroll
-                    for (int j = 0; j < TN / 2; j++)
-                        asm("fma.rn.f32x2 %0, %1, %2, %0;" : "+l"(acc2[i][j]) : "l"(a[i]), "l"(b[j]));
-            } else {
-                float a[TM], b[TN];
-#pragma unroll
-                for (int q = 0; q < QM; q++) {
-                    float4 v = *reinterpret_cast<const float4 *>(&As[cur][k][q * (BM / QM) + ty * 4]);
-                    a[q * 4 + 0] = v.x, a[q * 4 + 1] = v.y, a[q * 4 + 2] = v.z, a[q * 4 + 3] = v.w;
-                }
-#pragma unroll
-                for (int q = 0; q < QN; q++) {
-                    float4 v = *reinterpret_cast<const float4 *>(&Bs[cur][k][q * (BN / QN) + tx * 4]);
-                    b[q * 4 + 0] = v.x, b[q * 4 + 1] = v.y, b[q * 4 + 2] = v.z, b[q * 4 + 3] = v.w;
-                }
-#if REPDL_MM_ORDER == 0
-#pragma unroll
-                for (int i = 0; i < TM; i++)
-#pragma unroll
-                    for (int j = 0; j < TN; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
-#else
-#pragma unroll
-                for (int j = 0; j < TN; j++)
-#pragma unroll
-                    for (int i = 0; i < TM; i++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
-#endif
+            for (int q = 0; q < QM; q++) {
+                float4 v = *reinterpret_cast<const float4 *>(&As[cur][k][q * (BM / QM) + ty * 4]);
+                a[q * 4 + 0] = v.x, a[q * 4 + 1] = v.y, a[q * 4 + 2] = v.z, a[q * 4 + 3] = v.w;
             }
+#pragma unroll
+            for (int q = 0; q < QN; q++) {
+                float4 v = *reinterpret_cast<const float4 *>(&Bs[cur][k][q * (BN / QN) + tx * 4]);
+                b[q * 4 + 0] = v.x, b[q * 4 + 1] = v.y, b[q * 4 + 2] = v.z, b[q * 4 + 3] = v.w;
+            }
+#pragma unroll
+            for (int i = 0; i < TM; i++)
+#pragma unroll
+                for (int j = 0; j < TN; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
         }
         if (more) {
             la[(s + 1) % D].store(As[cur ^ 1], t);
@@ -286,13 +215,8 @@ sgemm_kernel(const float *__restrict__ A, const float *__restrict__ B, const Out
         for (int q = 0; q < QN; q++) {
             int col = n0 + q * (BN / QN) + tx * 4;
             float c[4];
-            if constexpr (kF2) {
-                asm("mov.b64 {%0,%1}, %2;" : "=f"(c[0]), "=f"(c[1]) : "l"(acc2[i][q * 2 + 0]));
-                asm("mov.b64 {%0,%1}, %2;" : "=f"(c[2]), "=f"(c[3]) : "l"(acc2[i][q * 2 + 1]));
-            } else {
 #pragma unroll
-                for (int j = 0; j < 4; j++) c[j] = acc[i][q * 4 + j];
-            }
+            for (int j = 0; j < 4; j++) c[j] = acc[i][q * 4 + j];
             for (int r = 0; r < out.n; r++) {
                 float *crow = out.p[r] + (int64_t)row * ldc;
                 if (vecC) {
@@ -316,7 +240,7 @@ int launch_one(const float *A, const float *B, const OutSet &C, int M, int N, in
     int64_t tiles = (int64_t)tilesM * tilesN;
     if (tiles > 0x7FFFFFFF) return REPDL_E_RANGE;
     auto kern = sgemm_kernel<BM, BN, TM, TN, A_KC, B_KC, VEC, MINB, D>;
-    constexpr int smem_bytes = 2 * BK * ((kF2 ? 2 : 1) * BM + 4 + BN + 4) * (int)sizeof(float);
+    constexpr int smem_bytes = 2 * BK * (BM + 4 + BN + 4) * (int)sizeof(float);
     static unsigned long long smem_done = 0;  // one mask per kernel instantiation
     int e = ensure_smem(kern, smem_bytes, &smem_done);
     if (e) return e;
@@ -324,17 +248,6 @@ int launch_one(const float *A, const float *B, const OutSet &C, int M, int N, in
                                                                       tilesM, tilesN, vecC);
     return launch_status();
 }
-
-#ifndef REPDL_MM_BM
-#define REPDL_MM_BM 128
-#define REPDL_MM_BN 256
-#define REPDL_MM_TM 8
-#define REPDL_MM_TN 16
-#endif
-#define REPDL_MM_BIG REPDL_MM_BM, REPDL_MM_BN, REPDL_MM_TM, REPDL_MM_TN
-#ifndef REPDL_MM_ALT
-#define REPDL_MM_ALT 1   // 0: never use the 192 x 128 configuration
-#endif
 
 template <bool A_KC, bool B_KC, bool VEC>
 int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, int K, int64_t lda,
@@ -347,25 +260,31 @@ int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, 
     // rounds up to whole waves and how much of the edge tiles is padding, so both are costed.
     const int64_t sms = sm_count();
     const int64_t tiles_a = (int64_t)((M + 191) / 192) * ((N + 127) / 128);
-    const int64_t tiles_b = (int64_t)((M + REPDL_MM_BM - 1) / REPDL_MM_BM) * ((N + REPDL_MM_BN - 1) / REPDL_MM_BN);
+    const int64_t tiles_b = (int64_t)((M + 127) / 128) * ((N + 255) / 256);
     if (tiles_a >= 2 * sms || tiles_b >= 2 * sms) {
         const double cost_a = (double)((tiles_a + sms - 1) / sms) * (192.0 * 128.0) / 1.033;
-        const double cost_b = (double)((tiles_b + sms - 1) / sms) * ((double)REPDL_MM_BM * REPDL_MM_BN);
-        if (REPDL_MM_ALT && tiles_a >= 2 * sms && (cost_a < cost_b || tiles_b < 2 * sms))
+        const double cost_b = (double)((tiles_b + sms - 1) / sms) * (128.0 * 256.0);
+        if (tiles_a >= 2 * sms && (cost_a < cost_b || tiles_b < 2 * sms))
             return launch_one<192, 128, 12, 8, A_KC, B_KC, VEC, 1>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
-        return launch_one<REPDL_MM_BIG, A_KC, B_KC, VEC, REPDL_MM_MINB_BIG>(A, B, C, M, N, K, lda,
-                                                                           ldb, ldc, vecC, st);
+        return launch_one<128, 256, 8, 16, A_KC, B_KC, VEC, 1>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
     }
     int64_t mid = (int64_t)((M + 127) / 128) * ((N + 63) / 64);
-    if (mid >= 2 * (int64_t)sm_count())
-        return launch_one<128, 64, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC,
-                                                             st);
+    if (mid >= 2 * sms)
+        return launch_one<128, 64, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
+    // Problems that cannot fill the machine twice: the largest tile that still gives most SMs a CTA.
+    // Measured on B200 (1024^3, L2 flushed): 64 x 128 tiles 28.3 TFLOP/s, 32 x 64 with two slabs in
+    // flight 27.2, 128 x 64 25.0, 64 x 64 24.4; 512 x 512 x 4096: 32 x 64 11.9 against 64 x 64 6.8.
+    const int64_t wide = (int64_t)((M + 63) / 64) * ((N + 127) / 128);
+    if (4 * wide >= 3 * sms)
+        return launch_one<64, 128, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
     // Few outputs but a long K (e.g. a 256 x 128 layer output over K = 9216): the time is K times
     // the instructions one warp issues per k-step, so spread the outputs over more, thinner CTAs.
-    int64_t small = (int64_t)((M + 63) / 64) * ((N + 63) / 64);
-    if (small * 4 <= (int64_t)sm_count() && K >= 1024)
+    const int64_t small = (int64_t)((M + 63) / 64) * ((N + 63) / 64);
+    if (small * 4 <= sms && K >= 1024)
         return launch_one<32, 32, 4, 4, A_KC, B_KC, VEC, 8, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
-    return launch_one<64, 64, 8, 8, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
+    if (4 * small >= 3 * sms)
+        return launch_one<64, 64, 8, 8, A_KC, B_KC, VEC, 8>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
+    return launch_one<32, 64, 4, 8, A_KC, B_KC, VEC, 8, 2>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
 }
 
 }  // namespace
