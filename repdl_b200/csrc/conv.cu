@@ -19,7 +19,7 @@
 //            identity for every accumulator except -0, and an accumulator that started at +0 can
 //            only become -0 when a non-zero product underflows to zero; so each CTA watches its
 //            operands while loading them and, if it meets a non-finite value or a non-zero value
-//            below 2^-74 (products of larger values cannot underflow to zero), discards its tile
+//            below 2^-51 (sums of products of larger values cannot round to zero), discards its tile
 //            and recomputes it with the direct form.  Wrong bits are therefore impossible, not
 //            merely unlikely.
 #include "common.cuh"
@@ -201,11 +201,15 @@ __device__ __noinline__ float conv2d_grad_input_exact(const float *__restrict__ 
 // ------------------------------------------------------------------------------------------------
 constexpr int CG_BK = 16, CG_BN = 128;
 
-// value needs the exact path: non-finite, or non-zero and so small that a product could vanish
+// Value needs the exact path: non-finite, or non-zero and below 2^-51.  With every non-zero operand
+// at least 2^-51 in magnitude every product is a multiple of 2^-102 and at least 2^-102, far above the
+// subnormal range, so no product underflows and no sum of such values can round to zero from a
+// non-zero exact value: an accumulator that started at +0 then never becomes -0 (an exact
+// cancellation gives +0), which is what makes a +0.0 padding tap the identity.
 __device__ __forceinline__ bool cg_unsafe(float v)
 {
     const unsigned ax = __float_as_uint(v) & 0x7FFFFFFFu;
-    return (ax - 1u < 0x1A7FFFFFu) || ax >= 0x7F800000u;  // 0 < |v| < 2^-74, or inf / NaN
+    return (ax - 1u < 0x25FFFFFFu) || ax >= 0x7F800000u;  // 0 < |v| < 2^-51, or inf / NaN
 }
 
 template <int BM, int MODE, bool S1>  // S1: stride 1 in both directions (no divisions in the gather)
@@ -430,6 +434,408 @@ conv_gemm_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, fl
     }
 }
 
+// ------------------------------------------------------------------------------------------------
+// Stride-1 3 x 3 convolutions through a staged source window (conv2d, and conv2d_grad_input, which
+// at stride 1 is a convolution of grad_output with the taps walked backwards).
+//
+// The on-the-fly im2col of conv_gemm_kernel costs address arithmetic, a load and an operand check
+// per GATHERED element, i.e. 9 times per source element.  Here a CTA owns a strip of R output rows
+// of one image for up to 64 output channels, and per chunk of 8 reduction planes it stages
+//   * the source window of the strip (R + 2 rows, padding materialised as +0.0): 4-byte cp.async
+//     copies from offsets that a thread computes once per CTA, and
+//   * the chunk's weights, read along k with 16-byte loads and scattered to [k][channel]
+// into double-buffered shared memory; every staged value is checked once.  The main loop then needs
+// no index arithmetic: a thread owns 8 channels x 2 groups of 4 consecutive pixels of a row; for one
+// (plane, kh) the 6 window values of a group arrive as two 16-byte loads and serve all 3 taps, so a
+// k-step is 64 FFMA for 2 loads of weights and 2/3 of a load of pixels.  k runs (plane, kh, kw)
+// ascending, the reference's chain order; planes past the end enter as (-0) * (+0) = -0, the
+// identity.  Padding as +0.0 is exact under the same operand watch and per-tile exact fallback as
+// conv_gemm_kernel.
+// ------------------------------------------------------------------------------------------------
+constexpr int CW_PC = 8;             // reduction planes per chunk
+constexpr int CW_KC = CW_PC * 9;     // k-steps per chunk
+
+struct WinGeom {
+    int M, planes;       // GEMM rows (output channels of this launch); reduction planes
+    int outH, outW;      // output image
+    int srcH, srcW;      // source image
+    int R, strips;       // output rows per strip; strips per image
+    int G4, pairs;       // 4-pixel groups per output row; pairs of groups per CTA
+    int WR, WP;          // window rows (R + 2); window pitch in floats (a multiple of 4)
+    int y_off, x_off;    // window (0, 0) is source (strip's first output row + y_off, x_off)
+    int active;          // threads that own outputs (OG * pairs); the rest only stage
+    int vecw;            // weights may be read with 16-byte loads
+};
+
+#ifndef REPDL_CW_MINB
+#define REPDL_CW_MINB 2
+#endif
+#ifndef REPDL_CW_UNROLL
+#define REPDL_CW_UNROLL 1
+#endif
+template <int MODE, int OG, int NTH>
+__global__ void __launch_bounds__(NTH, NTH <= 192 ? REPDL_CW_MINB : 1)
+conv_window_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, float *__restrict__ Out,
+                   ConvDims d, WinGeom w)
+{
+    constexpr int BM = OG * 8, PA = BM + 4;
+    constexpr int NWQ = (BM * CW_KC / 4 + NTH - 1) / NTH;  // 16-byte weight groups per thread
+    extern __shared__ __align__(16) float cw_smem[];
+    const int plane_floats = w.WR * w.WP;
+    const int win_floats = CW_PC * plane_floats;
+    const int stage_floats = win_floats + CW_KC * PA;
+    const int t = threadIdx.x;
+    constexpr int nt = NTH;
+    const int og = t % OG, pair = t / OG;
+    const int strip = blockIdx.x % w.strips, n = blockIdx.x / w.strips;
+    const int m0 = blockIdx.y * BM, g = blockIdx.z;
+    const int r0 = strip * w.R;
+    const int ICg = d.IC / d.groups, OCg = d.OC / d.groups;
+    const int64_t srcHW = (int64_t)w.srcH * w.srcW;
+    const float *src_n =
+        Src + ((int64_t)n * (MODE == 0 ? d.IC : d.OC) + (MODE == 0 ? g * ICg : 0)) * srcHW;
+    const int K = w.planes * 9;
+    const bool owner = t < w.active;
+
+    int grow[2], gcol[2];
+    bool gok[2];
+#pragma unroll
+    for (int h = 0; h < 2; h++) {
+        const int grp = pair + h * w.pairs;
+        gok[h] = owner && grp < w.R * w.G4;
+        const int gg = gok[h] ? grp : 0;
+        grow[h] = gg / w.G4;
+        gcol[h] = (gg - grow[h] * w.G4) * 4;
+    }
+    // where each window element comes from (the same for every plane): offset inside a source plane,
+    // or -1 for padding; a table in shared memory, filled once per CTA
+    int *woff = reinterpret_cast<int *>(cw_smem + 2 * stage_floats);
+    for (int e = t; e < plane_floats; e += nt) {
+        const int row = e / w.WP, col = e - row * w.WP;
+        const int sy = r0 + w.y_off + row, sx = w.x_off + col;
+        woff[e] = (sy >= 0 && sy < w.srcH && sx >= 0 && sx < w.srcW) ? sy * w.srcW + sx : -1;
+    }
+    __syncthreads();
+
+    auto stage_window = [&](int chunk, float *win) {
+        const float *sp = src_n + (int64_t)chunk * CW_PC * srcHW;
+        const int np = min(CW_PC, w.planes - chunk * CW_PC);  // planes of this chunk that exist
+        for (int e = t; e < plane_floats; e += nt) {
+            const int off = woff[e];
+            const float *s0 = sp + (off >= 0 ? off : 0);
+            float *dst = win + e;
+#pragma unroll
+            for (int p = 0; p < CW_PC; p++) {
+                const bool ok = off >= 0 && p < np;
+                cp_async_4_zfill(dst + p * plane_floats, ok ? s0 + p * srcHW : sp, ok);
+            }
+        }
+        cp_async_commit();
+    };
+    bool unsafe = false;
+    auto check_window = [&](const float *win) {
+        for (int e = t; e < plane_floats; e += nt) {
+#pragma unroll
+            for (int p = 0; p < CW_PC; p++) unsafe |= cg_unsafe(win[p * plane_floats + e]);
+        }
+    };
+    // weights of one chunk: global -> registers (16 bytes along k) -> As[k][channel]
+    float4 wq[NWQ];
+    auto load_weights_slow = [&](int chunk) {
+#pragma unroll
+        for (int i = 0; i < NWQ; i++) {
+            const int idx = t + i * nt;
+            wq[i] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            if (idx >= BM * (CW_KC / 4)) continue;
+            int ch, kl;
+            const float *src;
+            if (MODE == 0) {  // row (channel) of [OC][K], k contiguous
+                ch = idx / (CW_KC / 4), kl = (idx - ch * (CW_KC / 4)) * 4;
+                src = Kw + (int64_t)(g * OCg + m0 + ch) * K + chunk * CW_KC + kl;
+            } else {  // plane p = oc: a contiguous block [IC][9]; here j = ic * 9 + r
+                const int p = idx / (BM * 9 / 4), j = (idx - p * (BM * 9 / 4)) * 4;
+                ch = j, kl = p;  // decoded element by element below
+                src = Kw + ((int64_t)(chunk * CW_PC + p) * d.IC + m0) * 9 + j;
+            }
+            float v[4];
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                bool in;
+                if (MODE == 0)
+                    in = m0 + ch < w.M && chunk * CW_KC + kl + e < K;
+                else
+                    in = m0 + (ch + e) / 9 < w.M && chunk * CW_PC + kl < w.planes;
+                v[e] = 0.0f;
+                if (in && !w.vecw) v[e] = __ldg(src + e);
+            }
+            if (w.vecw) {
+                bool all;
+                if (MODE == 0)
+                    all = m0 + ch < w.M && chunk * CW_KC + kl + 3 < K;
+                else
+                    all = m0 + (ch + 3) / 9 < w.M && chunk * CW_PC + kl < w.planes;
+                if (all) {
+                    const float4 q = ldg_f4(src);
+                    v[0] = q.x, v[1] = q.y, v[2] = q.z, v[3] = q.w;
+                } else {
+#pragma unroll
+                    for (int e = 0; e < 4; e++) {
+                        bool in;
+                        if (MODE == 0)
+                            in = m0 + ch < w.M && chunk * CW_KC + kl + e < K;
+                        else
+                            in = m0 + (ch + e) / 9 < w.M && chunk * CW_PC + kl < w.planes;
+                        if (in) v[e] = __ldg(src + e);
+                    }
+                }
+            }
+            wq[i] = make_float4(v[0], v[1], v[2], v[3]);
+        }
+    };
+    auto store_weights_slow = [&](int chunk, float *As) {
+#pragma unroll
+        for (int i = 0; i < NWQ; i++) {
+            const int idx = t + i * nt;
+            if (idx >= BM * (CW_KC / 4)) continue;
+            const float v[4] = {wq[i].x, wq[i].y, wq[i].z, wq[i].w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                int ch, kl;
+                if (MODE == 0) {
+                    ch = idx / (CW_KC / 4), kl = (idx - ch * (CW_KC / 4)) * 4 + e;
+                } else {
+                    const int p = idx / (BM * 9 / 4), j = (idx - p * (BM * 9 / 4)) * 4 + e;
+                    ch = j / 9, kl = p * 9 + (j - ch * 9);
+                }
+                // past the last plane: (-0) * (+0) = -0, the identity; channels past M: zero rows
+                const bool ktail = chunk * CW_KC + kl >= K;
+                As[kl * PA + ch] = ktail ? -0.0f : v[e];
+                unsafe |= cg_unsafe(v[e]);
+            }
+        }
+    };
+
+    // The usual case -- a full tile of channels, a full chunk of planes, 16-byte aligned weight rows --
+    // works from offsets computed once per CTA: per group of 4 consecutive weights one global offset
+    // (relative to the chunk) and the shared-memory positions of its 4 elements.
+    const bool wfast = w.vecw && m0 + BM <= w.M;
+    int wg_off[NWQ], ws_off[NWQ][MODE == 0 ? 1 : 4];
+#pragma unroll
+    for (int i = 0; i < NWQ; i++) {
+        const int idx = t + i * nt;
+        wg_off[i] = -1;
+        if (idx < BM * (CW_KC / 4)) {
+            if (MODE == 0) {
+                const int ch = idx / (CW_KC / 4), kl = (idx - ch * (CW_KC / 4)) * 4;
+                wg_off[i] = (g * OCg + m0 + ch) * K + kl;
+                ws_off[i][0] = kl * PA + ch;
+            } else {
+                const int pp = idx / (BM * 9 / 4), j = (idx - pp * (BM * 9 / 4)) * 4;
+                wg_off[i] = (pp * d.IC + m0) * 9 + j;
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int ch = (j + e) / 9;
+                    ws_off[i][MODE == 0 ? 0 : e] = (pp * 9 + (j + e - ch * 9)) * PA + ch;
+                }
+            }
+        }
+    }
+    auto load_weights = [&](int chunk) {
+        if (!(wfast && (chunk + 1) * CW_PC <= w.planes)) {
+            load_weights_slow(chunk);
+            return;
+        }
+        const float *base = Kw + (MODE == 0 ? (int64_t)chunk * CW_KC : (int64_t)chunk * CW_PC * d.IC * 9);
+#pragma unroll
+        for (int i = 0; i < NWQ; i++)
+            if (wg_off[i] >= 0) wq[i] = ldg_f4(base + wg_off[i]);
+    };
+    auto store_weights = [&](int chunk, float *As) {
+        if (!(wfast && (chunk + 1) * CW_PC <= w.planes)) {
+            store_weights_slow(chunk, As);
+            return;
+        }
+#pragma unroll
+        for (int i = 0; i < NWQ; i++) {
+            if (wg_off[i] < 0) continue;
+            const float v[4] = {wq[i].x, wq[i].y, wq[i].z, wq[i].w};
+#pragma unroll
+            for (int e = 0; e < 4; e++) {
+                As[MODE == 0 ? ws_off[i][0] + e * PA : ws_off[i][MODE == 0 ? 0 : e]] = v[e];
+                unsafe |= cg_unsafe(v[e]);
+            }
+        }
+    };
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.0f;
+
+    const int nchunks = (w.planes + CW_PC - 1) / CW_PC;
+    stage_window(0, cw_smem);
+    load_weights(0);
+    store_weights(0, cw_smem + win_floats);
+    for (int c = 0; c < nchunks; c++) {
+        float *cur = cw_smem + (c & 1) * stage_floats, *nxt = cw_smem + ((c + 1) & 1) * stage_floats;
+        cp_async_wait<0>();
+        check_window(cur);
+        __syncthreads();  // chunk c is complete, and every thread has left chunk c - 1
+        const bool more = c + 1 < nchunks;
+        if (more) {
+            stage_window(c + 1, nxt);
+            load_weights(c + 1);
+        }
+        if (owner) {
+            // 24 (plane, kh) rows: the window rows of both pixel groups and the weight rows advance
+            // by constant strides (kh walks the window downwards for conv2d, upwards for grad_input)
+            const float *row0 = cur + (grow[0] + (MODE == 0 ? 0 : 2)) * w.WP + gcol[0];
+            const float *row1 = cur + (grow[1] + (MODE == 0 ? 0 : 2)) * w.WP + gcol[1];
+            const float *ak = cur + win_floats + og * 4;
+            const int step_kh = MODE == 0 ? w.WP : -w.WP;
+            const int step_p = plane_floats - 3 * step_kh;
+            constexpr int kUnroll = REPDL_CW_UNROLL;
+#pragma unroll kUnroll
+            for (int it = 0, kh = 0; it < CW_PC * 3; it++) {
+                float bq[2][8];
+                {
+                    const float4 v0 = *reinterpret_cast<const float4 *>(row0);
+                    const float4 v1 = *reinterpret_cast<const float4 *>(row0 + 4);
+                    const float4 u0 = *reinterpret_cast<const float4 *>(row1);
+                    const float4 u1 = *reinterpret_cast<const float4 *>(row1 + 4);
+                    bq[0][0] = v0.x, bq[0][1] = v0.y, bq[0][2] = v0.z, bq[0][3] = v0.w;
+                    bq[0][4] = v1.x, bq[0][5] = v1.y, bq[0][6] = v1.z, bq[0][7] = v1.w;
+                    bq[1][0] = u0.x, bq[1][1] = u0.y, bq[1][2] = u0.z, bq[1][3] = u0.w;
+                    bq[1][4] = u1.x, bq[1][5] = u1.y, bq[1][6] = u1.z, bq[1][7] = u1.w;
+                }
+#pragma unroll
+                for (int kw = 0; kw < 3; kw++) {
+                    const float4 a0 = *reinterpret_cast<const float4 *>(ak + kw * PA);
+                    const float4 a1 = *reinterpret_cast<const float4 *>(ak + kw * PA + BM / 2);
+                    const int o = MODE == 0 ? kw : 2 - kw;
+                    const float a[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+                    const float b[8] = {bq[0][o], bq[0][o + 1], bq[0][o + 2], bq[0][o + 3],
+                                        bq[1][o], bq[1][o + 1], bq[1][o + 2], bq[1][o + 3]};
+#pragma unroll
+                    for (int i = 0; i < 8; i++)
+#pragma unroll
+                        for (int j = 0; j < 8; j++) acc[i][j] = __fmaf_rn(a[i], b[j], acc[i][j]);
+                }
+                ak += 3 * PA;
+                const bool last_kh = ++kh == 3;
+                if (last_kh) kh = 0;
+                row0 += last_kh ? step_kh + step_p : step_kh;
+                row1 += last_kh ? step_kh + step_p : step_kh;
+            }
+        }
+        if (more) store_weights(c + 1, nxt + win_floats);
+    }
+    const bool redo = __syncthreads_or(unsafe ? 1 : 0) != 0;
+    if (!owner) return;
+
+    const int planes_out = MODE == 0 ? d.OC : d.IC;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + (i < 4 ? og * 4 + i : BM / 2 + og * 4 + i - 4);
+        if (m >= w.M) continue;
+        const int plane = MODE == 0 ? g * OCg + m : m;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int row = r0 + grow[h];
+            if (!gok[h] || row >= w.outH) continue;
+            float c[4] = {acc[i][h * 4 + 0], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]};
+            if (redo) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) {
+                    if (gcol[h] + j < w.outW)
+                        c[j] = MODE == 0 ? conv2d_exact(Src, Kw, d, n, plane, row, gcol[h] + j)
+                                         : conv2d_grad_input_exact(Src, Kw, d, n, plane, row, gcol[h] + j);
+                }
+            }
+            float *dst = Out + (((int64_t)n * planes_out + plane) * w.outH + row) * w.outW + gcol[h];
+            if (gcol[h] + 3 < w.outW && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
+                *reinterpret_cast<float4 *>(dst) = make_float4(c[0], c[1], c[2], c[3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++)
+                    if (gcol[h] + j < w.outW) dst[j] = c[j];
+            }
+        }
+    }
+}
+
+// Geometry and launch of conv_window_kernel; returns -1 when the shape is not one it takes.
+template <int MODE>
+int launch_conv_window(const float *src, const float *kw, float *out, const ConvDims &d, cudaStream_t st)
+{
+    if (d.sH != 1 || d.sW != 1 || d.KW != 3 || d.KH != 3) return -1;
+    WinGeom w{};
+    const int ICg = d.IC / d.groups, OCg = d.OC / d.groups;
+    w.M = MODE == 0 ? OCg : d.IC;
+    w.planes = MODE == 0 ? ICg : d.OC;
+    if (w.planes < CW_PC || w.M < 16) return -1;  // short chains / few channels: the gather kernel
+    w.outH = MODE == 0 ? d.OH : d.H, w.outW = MODE == 0 ? d.OW : d.W;
+    w.srcH = MODE == 0 ? d.H : d.OH, w.srcW = MODE == 0 ? d.W : d.OW;
+    w.y_off = MODE == 0 ? -d.pH : d.pH - 2;
+    w.x_off = MODE == 0 ? -d.pW : d.pW - 2;
+    w.G4 = (w.outW + 3) / 4;
+    w.WP = w.G4 * 4 + 4;  // a group reads 8 floats from its first pixel on
+    const int OG = w.M >= 48 ? 8 : 4, BM = OG * 8;
+    const int smem_limit = 100 * 1024;  // two CTAs per SM
+    // rows per strip: at least 128 owning threads where the image allows it (the staging of a chunk
+    // is shared by more outputs), then the fewest idle output slots
+    int bestR = 0;
+    double best = 0.0;
+    for (int R = 1; R <= w.outH; R++) {
+        const int pairs = (R * w.G4 + 1) / 2;
+        if (OG * pairs > 256) break;
+        const int64_t stage_floats = (int64_t)CW_PC * (R + 2) * w.WP + (int64_t)CW_KC * (BM + 4);
+        if ((2 * stage_floats + (int64_t)(R + 2) * w.WP) * 4 > smem_limit) break;
+        const int threads = OG * pairs <= 128 ? 128 : (OG * pairs <= 192 ? 192 : 256);
+        const int strips = (w.outH + R - 1) / R;
+        double eff = (double)w.outH * w.outW / ((double)strips * pairs * 8);
+        if (OG * pairs < 128) eff *= (double)(OG * pairs) / 128.0;
+        if (eff >= best - 1e-9) best = eff, bestR = R;  // ties: the taller strip
+    }
+    if (bestR == 0 || best < 0.55) return -1;
+    w.R = bestR;
+    w.strips = (w.outH + w.R - 1) / w.R;
+    w.pairs = (w.R * w.G4 + 1) / 2;
+    w.WR = w.R + 2;
+    w.active = OG * w.pairs;
+    const int threads = w.active <= 128 ? 128 : (w.active <= 192 ? 192 : 256);
+    // 16-byte weight loads: rows of [OC][K] (or blocks of [IC][9]) that start on 16-byte boundaries
+    const int K = w.planes * 9;
+    w.vecw = aligned16(kw) && (MODE == 0 ? (K % 4 == 0) : ((int64_t)d.IC * 9 % 4 == 0 && w.M % 4 == 0 && BM % 4 == 0));
+    if (MODE == 1 && (BM * 9) % 4 != 0) w.vecw = 0;
+    const int64_t gx = (int64_t)w.strips * d.N;
+    const int groups = MODE == 0 ? d.groups : 1;
+    const int gy = (w.M + BM - 1) / BM;
+    if (gx > 0x7FFFFFFF || gy > 65535 || groups > 65535) return -1;
+    const int smem = (int)((2 * ((int64_t)CW_PC * w.WR * w.WP + (int64_t)CW_KC * (BM + 4)) + (int64_t)w.WR * w.WP) * 4);
+    dim3 grid((unsigned)gx, (unsigned)gy, (unsigned)groups);
+#define REPDL_CW_LAUNCH(OGV, NTV)                                                                  \
+    do {                                                                                           \
+        static unsigned long long done = 0;                                                        \
+        /* opt in once for the largest size any shape may ask for, not for this shape's */         \
+        const int e = ensure_smem(conv_window_kernel<MODE, OGV, NTV>, smem_limit, &done);          \
+        if (e) return e;                                                                           \
+        conv_window_kernel<MODE, OGV, NTV><<<grid, NTV, smem, st>>>(src, kw, out, d, w);           \
+    } while (0)
+    if (OG == 8) {
+        if (threads == 128) REPDL_CW_LAUNCH(8, 128);
+        else if (threads == 192) REPDL_CW_LAUNCH(8, 192);
+        else REPDL_CW_LAUNCH(8, 256);
+    } else {
+        if (threads == 128) REPDL_CW_LAUNCH(4, 128);
+        else if (threads == 192) REPDL_CW_LAUNCH(4, 192);
+        else REPDL_CW_LAUNCH(4, 256);
+    }
+#undef REPDL_CW_LAUNCH
+    return launch_status();
+}
+
 template <int MODE>
 int launch_conv_gemm(const float *src, const float *kw, float *out, const ConvDims &d, cudaStream_t st)
 {
@@ -440,6 +846,10 @@ int launch_conv_gemm(const float *src, const float *kw, float *out, const ConvDi
     const int64_t gx = (ncols + CG_BN - 1) / CG_BN;
     const int groups = MODE == 0 ? d.groups : 1;
     if (gx > 0x7FFFFFFF || groups > 65535) return REPDL_E_RANGE;
+    {
+        const int e = launch_conv_window<MODE>(src, kw, out, d, st);
+        if (e >= 0) return e;
+    }
     (void)ICg;
     const bool s1 = d.sH == 1 && d.sW == 1;
     if (M <= 32) {

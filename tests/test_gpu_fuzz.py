@@ -85,6 +85,62 @@ def test_conv_and_gradients_random_shapes(cfg):
         assert same(fused[1].reshape(-1), oracle.sum4d_dim023(go).reshape(-1))
 
 
+def window_conv_configs(seed, count):
+    """Shapes of the stride-1, three-column kernels with many planes, which take the staged-window
+    kernel: strips that do not divide the image, rows that are not a multiple of 4 pixels, channel
+    counts around the 32 / 64-channel tiles, plane counts that are not a multiple of a chunk."""
+    rnd = random.Random(seed)
+    out = []
+    while len(out) < count:
+        N, IC, OC = rnd.randint(1, 4), rnd.randint(8, 40), rnd.randint(16, 72)
+        H, W = rnd.randint(3, 34), rnd.randint(3, 34)
+        KH = rnd.randint(1, 5)
+        pH, pW = rnd.choice([0, 0, 1, 2]), rnd.choice([0, 1, 1, 2])
+        if H + 2 * pH < KH or W + 2 * pW < 3:
+            continue
+        out.append((N, IC, H, W, OC, KH, 3, (1, 1), (pH, pW)))
+    return out
+
+
+@pytest.mark.parametrize("cfg", window_conv_configs(515, 24 * SCALE), ids=lambda c: "x".join(map(str, c[:7])) + "_p%d%d" % c[8])
+def test_conv_window_kernel_random_shapes(cfg):
+    from repdl_b200 import ops
+    N, IC, H, W, OC, KH, KW, s, p = cfg
+    g = torch.Generator().manual_seed(hash(cfg) & 0xFFFFFF)
+    OH, OW = H + 2 * p[0] - KH + 1, W + 2 * p[1] - KW + 1
+    x, k, go = _randn(g, N, IC, H, W), _randn(g, OC, IC, KH, KW), _randn(g, N, OC, OH, OW)
+    same = bits_equal
+    if (N + IC + H + W + OC) % 4 == 0:  # operands that force the exact fallback of some tiles
+        x.view(-1)[1::97] *= 1e-30
+        k.view(-1)[5::131] *= 1e-38
+        go.view(-1)[go.numel() // 3] = float("-inf")
+        same = equal_up_to_nan_payload
+    xd, kd, god = x.cuda(), k.cuda(), go.cuda()
+    assert same(ops.conv2d(xd, kd, s, p, 1), oracle.conv2d(x, k, s, p, 1))
+    assert same(ops.conv2d_grad_input(x.shape, kd, god, s, p), oracle.conv2d_grad_input(x.shape, k, go, s, p))
+    if IC % 2 == 0 and OC % 2 == 0:  # grouped forward convolution
+        k2 = k[:, :IC // 2].contiguous()
+        assert same(ops.conv2d(xd, k2.cuda(), s, p, 2), oracle.conv2d(x, k2, s, p, 2))
+
+
+def test_conv_padding_keeps_a_negative_zero():
+    """An accumulator can become -0 without any operand being tiny enough for its products to vanish:
+    -3 * 2^-149 plus (3 - 2^-22) * 2^-149 rounds to -0.  The padding tap behind it must then leave
+    -0 alone (the reference skips it), so operands this small have to take the exact path."""
+    from repdl_b200 import ops
+    a, b = 1.5 * 2.0 ** -74, (1.5 - 2.0 ** -23) * 2.0 ** -74
+    # (1 plane, 1 x 3 taps): the gather kernel; (8 planes, 3 x 3 taps): the staged-window kernel.  The
+    # two values sit at the end of the last row of the last plane, so that only padding taps follow.
+    for IC, OC, KH in ((1, 2, 1), (8, 16, 3)):
+        x = torch.zeros(2, IC, 8, 64)
+        k = torch.zeros(OC, IC, KH, 3)
+        x[:, IC - 1, 7, 62], x[:, IC - 1, 7, 63] = a, b
+        k[:, IC - 1, KH // 2, 0], k[:, IC - 1, KH // 2, 1], k[:, IC - 1, KH // 2, 2] = -(2.0 ** -74), 2.0 ** -74, 1.0
+        want = oracle.conv2d(x, k, (1, 1), (KH // 2, 1), 1)
+        assert want[0, 0, 7, 63].view(torch.int32).item() == -2 ** 31  # -0.0 in the corner
+        assert bits_equal(ops.conv2d(x.cuda(), k.cuda(), (1, 1), (KH // 2, 1), 1), want)
+
+
 def mm_shapes(seed, count):
     rnd = random.Random(seed)
     return [(rnd.randint(1, 420), rnd.randint(1, 420), rnd.choice([0, 1, 15, 16, 17, rnd.randint(1, 700)]),
