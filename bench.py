@@ -719,14 +719,27 @@ def main():
                else (a_host.numel() + b_host.numel()) * 4,
                "d2h_bytes_per_step": world * c_host.numel() * 4}
 
-    # parity of the timed result against the golden hash of the reference CPU backend
+    # parity of the timed result against the hashes of the reference CPU backend's own product
+    # (tests/golden/mm16k.json): rank 0 hashes the whole gathered C; with several ranks every rank
+    # also hashes the rows IT computed, as they lie in ITS copy of C, against the per-block hashes
     parity = None
-    if rank == 0:
-        gpath = os.path.join(ROOT, "tests", "golden", "mm16k.json")
-        if n == 16384 and os.path.exists(gpath):
-            gold = json.load(open(gpath))
+    gpath = os.path.join(ROOT, "tests", "golden", "mm16k.json")
+    if n == 16384 and os.path.exists(gpath):
+        gold = json.load(open(gpath))
+        mine_ok = 1
+        if world > 1 and Mp % 2048 == 0:
+            for blk in range(Mp // 2048):
+                r0 = rank * Mp + blk * 2048
+                h = hashlib.sha256(sh.C[r0:r0 + 2048].cpu().numpy().tobytes()).hexdigest()
+                mine_ok &= int(h == gold["row_block_2048_sha256"][r0 // 2048])
+            t = torch.tensor([mine_ok], dtype=torch.int32, device=dev)
+            dist.all_reduce(t, op=dist.ReduceOp.MIN)
+            mine_ok = int(t[0])
+        if rank == 0:
             h = hashlib.sha256(sh.C.cpu().numpy().tobytes()).hexdigest()
-            parity = "sha256 equal to reference CPU backend" if h == gold["sha256"] else "MISMATCH"
+            ok = h == gold["sha256"] and mine_ok == 1
+            parity = ("sha256 equal to reference CPU backend" + (
+                "; every rank's own row blocks too" if world > 1 and Mp % 2048 == 0 else "")) if ok else "MISMATCH"
 
     if rank == 0:
         hbm_peak, peak_kind = measured_peaks()

@@ -100,8 +100,10 @@ __device__ __forceinline__ float4 apply4(const Op &op, float4 v, SmemTables tab)
 constexpr int EW_THREADS = 256;
 constexpr int EW_VEC_PER_THREAD = 4;  // float4 groups in flight per thread per iteration
 
+// (at least four CTAs per SM: log would otherwise take 68 registers and run three; measured 0.72 ->
+// 0.76 of the HBM peak)
 template <class Op>
-__global__ void __launch_bounds__(EW_THREADS)
+__global__ void __launch_bounds__(EW_THREADS, 4)
 unary_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t nvec, Op op)
 {
     // nvec = number of float4 groups; x and y are 16-byte aligned
