@@ -54,10 +54,61 @@ def _concurrently(*thunks):
     return out
 
 
+# Work of a backward pass that nothing else in that pass waits for (weight and bias gradients):
+# side streams that are only joined when the backward pass ends.
+_late = {}
+_pending = []
+
+
+def _join_deferred():
+    """End-of-backward callback: the stream that ran the backward pass waits for the deferred work."""
+    while _pending:
+        main, done = _pending.pop()
+        main.wait_event(done)
+
+
+def _deferred(thunk, reads, params):
+    """Runs thunk() -- operator calls whose results only the optimizer will read -- on a side stream
+    and returns at once; the calling stream is made to wait for it when the backward pass ends
+    (autograd's end-of-pass callbacks), so that the latency-bound weight-gradient chains of one layer
+    overlap the backward of the layers below it.  Only used when the results are not consumed
+    during the pass: every parameter in `params` must have no gradient yet (autograd then just
+    keeps the tensor; accumulating into an existing gradient would read it at once).  Returns None
+    if that does not hold, or outside a backward pass: the caller then computes in stream order.
+    `reads` are the tensors the side stream reads: the allocator must not recycle them for this
+    stream's later allocations before the side stream is done with them."""
+    if any(p is not None and p.grad is not None for p in params):
+        return None
+    main = torch.cuda.current_stream()
+    try:  # (queued on every deferral: the callback drains the list, extra calls find it empty)
+        torch.autograd.Variable._execution_engine.queue_callback(_join_deferred)
+    except Exception:  # not inside a backward pass of the autograd engine
+        return None
+    key = (main.device.index, main.cuda_stream)
+    ring = _late.setdefault(key, {"streams": [torch.cuda.Stream(device=main.device) for _ in range(3)], "next": 0})
+    stream = ring["streams"][ring["next"] % len(ring["streams"])]
+    ring["next"] += 1
+    ready = torch.cuda.Event()
+    ready.record(main)
+    stream.wait_event(ready)
+    with torch.cuda.stream(stream):
+        out = thunk()
+    for t in reads:
+        t.record_stream(stream)
+    for t in (out if isinstance(out, (tuple, list)) else (out,)):
+        if t is not None:
+            t.record_stream(main)
+    done = torch.cuda.Event()
+    done.record(stream)
+    _pending.append((main, done))
+    return out
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias):
         ctx.save_for_backward(x, weight)
+        ctx.bias_ref = bias
         out = ops.mm(x, weight, transB=True)       # x [B,in] times weight[out,in]^T
         if bias is not None:
             out += bias
@@ -69,10 +120,13 @@ class _Linear(torch.autograd.Function):
         gx = gw = gb = None
         if ctx.needs_input_grad[0]:
             gx = ops.mm(g, weight)
-        if ctx.needs_input_grad[1]:
-            gw = ops.mm(g, x, transA=True)
-        if ctx.needs_input_grad[2]:
-            gb = ops.sum2d_dim0(g)
+
+        def param_grads():
+            w = ops.mm(g, x, transA=True) if ctx.needs_input_grad[1] else None
+            b = ops.sum2d_dim0(g) if ctx.needs_input_grad[2] else None
+            return w, b
+        late = _deferred(param_grads, (g, x), (weight, ctx.bias_ref)) if ctx.needs_input_grad[1] else None
+        gw, gb = late if late is not None else param_grads()
         return gx, gw, gb
 
 
@@ -91,6 +145,7 @@ class _Conv2d(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, weight, bias, stride, padding, groups):
         ctx.save_for_backward(x, weight)
+        ctx.bias_ref = bias
         ctx.cfg = (stride, padding, groups)
         out = ops.conv2d(x, weight, stride, padding, groups)
         if bias is not None:
@@ -104,6 +159,14 @@ class _Conv2d(torch.autograd.Function):
             raise NotImplementedError("grouped convolution has no backward (as in the reference)")
         x, weight = ctx.saved_tensors
         need = ctx.needs_input_grad
+        if need[1] and need[2]:
+            # the weight / bias gradient chains go to a side stream that is only joined at the end
+            # of the backward pass; the input gradient, which the layers below wait for, runs here
+            late = _deferred(lambda: ops.conv2d_grad_kernel_bias(x, weight.shape, g, stride, padding),
+                             (g, x), (weight, ctx.bias_ref))
+            if late is not None:
+                gx = ops.conv2d_grad_input(x.shape, weight, g, stride, padding) if need[0] else None
+                return gx, late[0], late[1], None, None, None
         if need[1] and need[2]:
             # weight and bias gradient from one pass over g (the bias chain rides on the row operand of
             # the weight-gradient kernel); the input gradient overlaps on a side stream
