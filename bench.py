@@ -129,7 +129,11 @@ def event_ms(fn, stream=None):
 def ffma_peak_tflops(fp64=False):
     """FP32 (or FP64) FMA-pipe peak of the current GPU from the library's probe kernel."""
     import ctypes
-    from repdl_b200._cabi import check, lib
+    from repdl_b200._cabi import check
+    from repdl_b200.build import PROBE_LIB
+    lib = ctypes.CDLL(PROBE_LIB)  # the probe kernel is a benchmark helper, not part of the operator ABI
+    lib.repdl_b200_probe_fma.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
+                                         ctypes.POINTER(ctypes.c_double), ctypes.c_void_p]
     out = torch.zeros(4, dtype=torch.float64, device="cuda")
     flops = ctypes.c_double(0)
     iters = 1 << (14 if fp64 else 16)

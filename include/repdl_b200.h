@@ -189,15 +189,6 @@ int repdl_b200_adam_step(float *const *params, const float *const *grads, float 
                          float beta2, float one_minus_beta2, float sqrt_bias_correction2, float eps,
                          float neg_step_size, float weight_decay, void *stream);
 
-/* ---- diagnostics (no counterpart in the reference) --------------------------------------------
- * Enqueues a kernel of nothing but independent FMAs on every SM (fp64 == 0: scalar fp32 FFMA,
- * 1: fp64 DFMA, 2: packed fp32 fma.rn.f32x2 -- two FMAs per instruction):
- * blocks_per_sm * SMs CTAs of 256 threads, 16 * iters FMAs per thread.  *flops_issued (host
- * pointer, may be NULL) receives 2 * FMAs.  Time it with events to get the FMA-pipe peak of this
- * GPU at its current clocks.  scratch_out: 8 device bytes, never actually written. */
-int repdl_b200_probe_fma(int fp64, int iters, int blocks_per_sm, void *scratch_out,
-                         double *flops_issued, void *stream);
-
 #ifdef __cplusplus
 }
 #endif

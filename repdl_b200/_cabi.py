@@ -41,7 +41,6 @@ SIGNATURES = {
     "repdl_b200_div": (_int, [_ptr, _ptr, _ptr, _i64, _ptr]),
     "repdl_b200_softmax": (_int, [_ptr, _ptr, _i64, _i64, _ptr]),
     "repdl_b200_cross_entropy": (_int, [_ptr, _ptr, _ptr, _i64, _i64, _ptr, _ptr]),
-    "repdl_b200_probe_fma": (_int, [_int, _int, _int, _ptr, ctypes.POINTER(ctypes.c_double), _ptr]),
 }
 
 

@@ -2,6 +2,7 @@
 
   librepdl_b200.so            the CUDA kernels behind the C ABI of include/repdl_b200.h
                               (nvcc, sm_100a only, no torch dependency)
+  librepdl_b200_probe.so      benchmark helper (an FMA-pipe peak probe kernel), loaded by bench.py only
   backend/cuda*.so            the PyTorch extension that registers those kernels under the
                               names microsoft/RepDL's backend/cuda/bind.cpp:12-19 exports, so that
                               it can stand in for `repdl.backend.cuda`
@@ -17,6 +18,7 @@ import sysconfig
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIB = os.path.join(HERE, "librepdl_b200.so")
+PROBE_LIB = os.path.join(HERE, "librepdl_b200_probe.so")
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 
 # Numerics flags are part of the contract: no implicit FMA contraction, no flush-to-zero,
@@ -56,6 +58,11 @@ def build_lib(force=False, verbose=False):
     if force or procs or _newer(LIB, objs):
         subprocess.run([NVCC, "-shared", "-o", LIB, *objs, "-ccbin", "/usr/bin/g++",
                         "-cudart", "shared"], check=True)
+    # the benchmark's peak probe: a library of its own, outside the operator ABI
+    probe_src = os.path.join(CSRC, "probe", "probe.cu")
+    if force or _newer(PROBE_LIB, [probe_src] + hdrs):
+        subprocess.run([NVCC, *NVCC_FLAGS, "-shared", "-o", PROBE_LIB, probe_src, "-cudart", "shared"],
+                       check=True)
     return LIB
 
 

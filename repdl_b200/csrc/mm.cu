@@ -272,11 +272,12 @@ int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, 
     if (mid >= 2 * sms)
         return launch_one<128, 64, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
     // Problems that cannot fill the machine twice: the largest tile that still gives most SMs a CTA.
-    // Measured on B200 (1024^3, L2 flushed): 64 x 128 tiles 28.3 TFLOP/s, 32 x 64 with two slabs in
-    // flight 27.2, 128 x 64 25.0, 64 x 64 24.4; 512 x 512 x 4096: 32 x 64 11.9 against 64 x 64 6.8.
+    // Measured on B200 (1024^3, L2 flushed): 64 x 128 tiles 30.4 TFLOP/s (24.4 when the register
+    // budget is cut to four CTAs per SM), 32 x 64 with two slabs in flight 27.2, 128 x 64 25.0,
+    // 64 x 64 24.4; 512 x 512 x 4096: 32 x 64 11.9 against 64 x 64 6.8.
     const int64_t wide = (int64_t)((M + 63) / 64) * ((N + 127) / 128);
     if (4 * wide >= 3 * sms)
-        return launch_one<64, 128, 8, 8, A_KC, B_KC, VEC, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
+        return launch_one<64, 128, 8, 8, A_KC, B_KC, VEC, 2>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
     // Few outputs but a long K (e.g. a 256 x 128 layer output over K = 9216): the time is K times
     // the instructions one warp issues per k-step, so spread the outputs over more, thinner CTAs.
     const int64_t small = (int64_t)((M + 63) / 64) * ((N + 63) / 64);

@@ -1,7 +1,10 @@
+// BENCHMARK HELPER, not part of the operator library: built into its own shared object
+// (librepdl_b200_probe.so), which only bench.py loads.
+//
 // Peak-rate probes: dependent-free FFMA / DFMA loops that keep every FMA lane of the GPU busy.
 // bench.py times them to obtain the FP32 (and FP64) FMA-pipe peak of the very GPU, clocks and
 // power state the benchmark runs on; the GEMM roofline is quoted against that number.
-#include "common.cuh"
+#include "../common.cuh"
 
 namespace repdl_b200 {
 namespace {
@@ -64,7 +67,9 @@ extern "C" int repdl_b200_probe_fma(int fp64, int iters, int blocks_per_sm, void
     clear_stale_error();
     if (iters <= 0 || blocks_per_sm <= 0) return REPDL_E_SHAPE;
     if (!scratch_out) return REPDL_E_NULL;
-    unsigned blocks = (unsigned)(sm_count() * blocks_per_sm);
+    int dev = 0, sms = kNumSMsB200;
+    if (cudaGetDevice(&dev) == cudaSuccess) (void)cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    unsigned blocks = (unsigned)(sms * blocks_per_sm);
     if (fp64 == 2) {
         fma2_probe_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((float *)scratch_out, iters, 1.0f);
         if (flops_issued) *flops_issued = 4.0 * 16.0 * (double)iters * 256.0 * (double)blocks;

@@ -258,3 +258,31 @@ def cross_entropy(input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
         check(lib.repdl_b200_cross_entropy(x.data_ptr(), t.data_ptr(), out.data_ptr(), x.shape[0],
                                            x.shape[1], rows.data_ptr(), _stream(x)), "cross_entropy")
     return out
+
+
+def _with_nvtx_ranges():
+    """REPDL_B200_NVTX=1: every public operator runs inside an NVTX range named after it, so that a
+    timeline profiler shows which operator each kernel belongs to (off by default: the ranges cost
+    two host calls per operator)."""
+    import functools
+    import os
+    if os.environ.get("REPDL_B200_NVTX", "0") != "1":
+        return
+    names = ["mm", "conv2d", "conv2d_grad_input", "conv2d_grad_kernel", "conv2d_grad_kernel_bias",
+             "sum1d", "sum2d_dim0", "sum2d_dim1", "sum4d_dim023", "exp", "log", "sqrt", "div",
+             "softmax", "cross_entropy"]
+
+    def ranged(fn, label):
+        @functools.wraps(fn)
+        def wrapper(*args, **kwargs):
+            torch.cuda.nvtx.range_push(label)
+            try:
+                return fn(*args, **kwargs)
+            finally:
+                torch.cuda.nvtx.range_pop()
+        return wrapper
+    for n in names:
+        globals()[n] = ranged(globals()[n], "repdl_b200." + n)
+
+
+_with_nvtx_ranges()

@@ -125,3 +125,74 @@ def test_reference_python_layers_run_unchanged_on_the_dropin():
     for rec in got:
         assert rec["logits"] == want[rec["step"]]["logits"], rec["step"]
         assert rec["params"] == want[rec["step"]]["params"], rec["step"]
+
+
+BN_DROPIN = r"""
+import json, sys, torch
+sys.path.insert(0, {root!r})
+import repdl_b200
+repdl_b200.install()
+sys.path.insert(0, {site!r})
+import repdl, repdl.func
+sys.path.insert(0, {tests!r})
+from cases import sha
+res = {{}}
+# the mean functions behind batch norm (repdl/func.py:47-121), forward and backward
+g = torch.Generator().manual_seed(8)
+for name, fn, shape in (("mean1d", repdl.func.mean1d, (4097,)), ("mean2d_dim0", repdl.func.mean2d_dim0, (129, 70)),
+                        ("mean2d_dim0_wide", repdl.func.mean2d_dim0, (33, 1025)),
+                        ("mean4d_dim023", repdl.func.mean4d_dim023, (9, 5, 13, 11)),
+                        ("mean4d_dim023_big", repdl.func.mean4d_dim023, (16, 32, 26, 26))):
+    x = (torch.randn(*shape, generator=g) * 3 + 0.5)
+    w = torch.randn(*shape, generator=g)
+    out = []
+    for dev in ("cpu", "cuda"):
+        xi = x.detach().clone().to(dev).requires_grad_(True)
+        y = fn(xi)
+        try:  # (the reference's own mean2d_dim0 backward raises on a shape error, on either backend)
+            y.backward(torch.ones_like(y))
+            gsha = sha(xi.grad)
+        except RuntimeError:
+            gsha = "backward raises"
+        out.append((sha(y.detach()), gsha))
+    res[name] = out[0] == out[1]
+# BatchNorm2d of the reference on both backends: training steps (batch statistics, running statistics
+# updated), then evaluation with the running statistics; several shapes
+for tag, (N, C, H, W) in (("bn_small", (10, 8, 6, 6)), ("bn_odd", (7, 5, 9, 4)), ("bn_cnn", (32, 32, 26, 26)), ("bn_wide", (2, 3, 5, 40))):
+    outs = []  # (one channel: the reference's own expand_as raises, on either backend)
+    for dev in ("cpu", "cuda"):
+        torch.manual_seed(11)
+        bn = repdl.from_torch_module(torch.nn.Sequential(torch.nn.BatchNorm2d(C))).to(dev)
+        gi = torch.Generator().manual_seed(12)
+        rec = []
+        for it in range(2):
+            xi = (torch.randn(N, C, H, W, generator=gi) * 2 + 1).to(dev).requires_grad_(True)
+            yi = bn(xi)
+            yi.backward(torch.randn(N, C, H, W, generator=gi).to(dev))
+            rec += [sha(yi.detach()), sha(xi.grad)] + [sha(p.grad) for p in bn.parameters()]
+            with torch.no_grad():
+                for p in bn.parameters():
+                    p.add_(p.grad.mul(-0.1)); p.grad = None
+        rec += [sha(b) for b in bn.buffers() if b.dtype == torch.float32]
+        bn.eval()
+        with torch.no_grad():
+            rec.append(sha(bn((torch.randn(N, C, H, W, generator=gi)).to(dev))))
+        outs.append(rec)
+    res[tag] = outs[0] == outs[1]
+print(json.dumps(res))
+"""
+
+
+def test_reference_batch_norm_and_means_on_the_dropin():
+    """The reference's BatchNorm2d (repdl/nn/batchnorm.py:12-97) and the mean functions under it
+    (repdl/func.py:47-121), unmodified, on this package's kernels: forward, backward, running
+    statistics and evaluation mode give the bits of the reference's own CPU backend."""
+    import oracle
+    site = oracle.ref_site()
+    if site is None:
+        pytest.skip("the reference's Python package is not installed under oracle/_ref")
+    code = BN_DROPIN.format(root=ROOT, site=site, tests=os.path.join(ROOT, "tests"))
+    res = subprocess.run([sys.executable, "-c", code], capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stderr[-2000:]
+    got = json.loads(res.stdout.strip().splitlines()[-1])
+    assert len(got) == 9 and all(got.values()), got
