@@ -103,7 +103,10 @@ constexpr int EW_VEC_PER_THREAD = 4;  // float4 groups in flight per thread per 
 // (at least four CTAs per SM: log would otherwise take 68 registers and run three; measured 0.72 ->
 // 0.76 of the HBM peak)
 template <class Op>
-__global__ void __launch_bounds__(EW_THREADS, 4)
+#ifndef REPDL_EW_MINB
+#define REPDL_EW_MINB 4
+#endif
+__global__ void __launch_bounds__(EW_THREADS, REPDL_EW_MINB)
 unary_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t nvec, Op op)
 {
     // nvec = number of float4 groups; x and y are 16-byte aligned
