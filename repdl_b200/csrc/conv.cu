@@ -1060,18 +1060,32 @@ conv_gk_kernel(const float *__restrict__ GO, const float *__restrict__ I, float 
 // conv2d_grad_kernel, row-chunk form (the one used whenever an image's output rows give chunks of a
 // useful length).  Same split of roles as above -- warps that only multiply, one chain per thread, and
 // 8 warps that only stage -- but the staging warps never touch a value: k is walked image by image in
-// chunks of R whole output rows (or of <= 256 columns of one row when rows are longer than that),
-// every operand element goes global -> shared with one 4-byte cp.async (16-byte for grad_output when
-// its rows allow it), three chunks are in flight, and the (row, column) decoding of a thread's
-// elements is the same for every chunk, so it is done once.  What is left per element is the address
-// and the copy.  Padding taps are zero-filled by the copy itself (src-size 0), so only a padded
+// chunks of R whole output rows -- the whole image when that fits, up to 768 steps -- or of segments
+// of one row when rows are longer than that, every operand element goes global -> shared with one
+// 4-byte cp.async (16-byte for grad_output when its rows allow it), three chunks are in flight, and
+// the (row, column) decoding of a thread's elements is the same for every chunk, so it is done once.
+// What is left per element is the address and the copy.  Padding taps are zero-filled by the copy itself (src-size 0), so only a padded
 // convolution needs the operand watch: there the staging threads read back what they copied when it
 // has landed, and the CTA falls back to the exact loop for its outputs if a non-finite or vanishing
 // value was seen.  A CTA's tile is 8 output channels x 16 weight columns (4 multiplying warps), or
 // 4 x 8 (one warp) when there are so few outputs that the larger tile would leave most SMs idle.
 // ------------------------------------------------------------------------------------------------
-constexpr int GKR_KMAX = 256, GKR_PITCH = GKR_KMAX + 4, GKR_STAGES = 3;
+constexpr int GKR_RING = 6;     // groups of 4 steps a multiplying warp loads ahead of its FMAs
+constexpr int GKR_STAGES = 3;
+constexpr int GKR_KPT = 3;      // steps of a chunk that one staging thread copies, at most
+// steps of a chunk after padding to whole rings
+__host__ __device__ constexpr int gkr_padded(int len) { return (len + 4 * GKR_RING - 1) / (4 * GKR_RING) * (4 * GKR_RING); }
+// row pitch in floats for chunks of at most kmax steps: room for the padded chunk, a multiple of 4
+// (16-byte loads), and 4 or 12 modulo 32 so that the 16-byte segments of 4 rows or 8 columns at one
+// k fall into different banks
+static int gkr_pitch(int kmax)
+{
+    int p = gkr_padded(kmax);
+    while (p % 32 != 4 && p % 32 != 12) p += 4;
+    return p;
+}
 constexpr int GKR_STAGERS = 256;  // staging threads (8 warps)
+constexpr int GKR_KMAX = GKR_KPT * GKR_STAGERS;  // longest chunk
 
 __device__ __forceinline__ void cp_async_4(float *smem_dst, const float *gmem_src)
 {
@@ -1096,14 +1110,14 @@ struct GkChunk {
 // the chains consume anyway, in the order n, oh, ow of the reference's sum4d_dim023 -- and write the
 // bias gradient, which saves the separate pass over grad_output.
 template <bool PADDED, int RW, int CB, bool BIAS>
-__global__ void __launch_bounds__((RW * CB) * 32 + GKR_STAGERS)
+__global__ void __launch_bounds__((RW * CB) * 32 + GKR_STAGERS, 2)
 conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, float *__restrict__ GK,
-                    float *__restrict__ GB, ConvDims d, int segW, int R, int a16, long long nchunks)
+                    float *__restrict__ GB, ConvDims d, int segW, int R, int pitch, int a16, long long nchunks)
 {
     extern __shared__ __align__(16) float gkr_smem[];
     constexpr int ROWS = 4 * RW, COLS = 8 * CB, NCW = RW * CB;
     constexpr int NT = NCW * 32 + GKR_STAGERS;
-    constexpr int STAGE = (ROWS + COLS) * GKR_PITCH;
+    const int STAGE = (ROWS + COLS) * pitch;
     const bool producer = threadIdx.x >= NCW * 32;
     const int t = producer ? threadIdx.x - NCW * 32 : threadIdx.x;  // index within the role
     const int KHW = d.KH * d.KW, OHW = d.OH * d.OW, HW = d.H * d.W;
@@ -1140,12 +1154,17 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
     const int crow = 4 * (cw / CB) + prow, ccol = 8 * (cw % CB) + pcol;
 
     if (producer) {
-        // Thread t copies step k_local = t of every row and column of a chunk.  Rows and columns past
-        // the end are clamped to the last valid one: they are copied twice and feed outputs nobody
-        // stores, which is cheaper than predicating every copy.
-        const int sr = t / segW, sc = t - sr * segW;
-        const int boff = sr * d.sH * d.W + sc * d.sW;
-        const int hb = sr * d.sH - d.pH, wb = sc * d.sW - d.pW;
+        // Thread t copies steps t, t + 256, ... of every row and column of a chunk (GKR_KPT of them at
+        // most).  Rows and columns past the end are clamped to the last valid one: they are copied
+        // twice and feed outputs nobody stores, which is cheaper than predicating every copy.
+        int boff[GKR_KPT], hb[GKR_KPT], wb[GKR_KPT];
+#pragma unroll
+        for (int m = 0; m < GKR_KPT; m++) {
+            const int k = t + m * GKR_STAGERS;
+            const int sr = k / segW, sc = k - sr * segW;
+            boff[m] = sr * d.sH * d.W + sc * d.sW;
+            hb[m] = sr * d.sH - d.pH, wb[m] = sc * d.sW - d.pW;
+        }
         int col_off[COLS], col_hw[COLS];
 #pragma unroll
         for (int c = 0; c < COLS; c++) {
@@ -1156,65 +1175,71 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
             col_hw[c] = (kh << 16) | kw;
         }
         // 16-byte copies of grad_output: LPR threads per row, along k
-        constexpr int LPR = GKR_STAGERS / ROWS, A16M = (GKR_KMAX / 4 + LPR - 1) / LPR;
+        constexpr int LPR = GKR_STAGERS / ROWS;
         const int a16r = t / LPR, a16l = t % LPR;
         const int a16src = min(oc0 + a16r, d.OC - 1) - oc0;
 
         auto issue = [&](int st, const GkChunk &c) {
-            float *As = gkr_smem + st * STAGE, *Bs = As + ROWS * GKR_PITCH;
+            float *As = gkr_smem + st * STAGE, *Bs = As + ROWS * pitch;
             const int len = chunk_len(c);
             const float *ga = GO + ((int64_t)c.n * d.OC + oc0) * OHW + c.oh0 * d.OW + c.ow0;
             if (a16) {
                 const float *src = ga + (int64_t)a16src * OHW;
-#pragma unroll
-                for (int m = 0; m < A16M; m++) {
-                    const int q = 4 * (a16l + LPR * m);
-                    if (q < len) cp_async_16(&As[a16r * GKR_PITCH + q], src + q);
-                }
-            } else if (t < len) {
-#pragma unroll
-                for (int row = 0; row < ROWS; row++) {
-                    const int rr = min(oc0 + row, d.OC - 1) - oc0;
-                    cp_async_4(&As[row * GKR_PITCH + t], ga + (int64_t)rr * OHW + t);
-                }
+                for (int q = 4 * a16l; q < len; q += 4 * LPR) cp_async_16(&As[a16r * pitch + q], src + q);
             }
-            if (t < len) {
-                const float *gi =
-                    I + ((int64_t)c.n * d.IC * HW + (c.oh0 * d.sH) * d.W + c.ow0 * d.sW + boff);
-                const int hj = c.oh0 * d.sH + hb, wj = c.ow0 * d.sW + wb;
+            const float *gi = I + ((int64_t)c.n * d.IC * HW + (c.oh0 * d.sH) * d.W + c.ow0 * d.sW);
+#pragma unroll 1
+            for (int m = 0; m < GKR_KPT; m++) {
+                const int k = t + m * GKR_STAGERS;
+                if (k >= len) break;
+                if (!a16) {
+#pragma unroll
+                    for (int row = 0; row < ROWS; row++) {
+                        const int rr = min(oc0 + row, d.OC - 1) - oc0;
+                        cp_async_4(&As[row * pitch + k], ga + (int64_t)rr * OHW + k);
+                    }
+                }
+                const float *gim = gi + boff[m];
+                const int hj = c.oh0 * d.sH + hb[m], wj = c.ow0 * d.sW + wb[m];
 #pragma unroll
                 for (int cc = 0; cc < COLS; cc++) {
                     if (PADDED) {
                         const bool ok = (unsigned)(hj + (col_hw[cc] >> 16)) < (unsigned)d.H &&
                                         (unsigned)(wj + (col_hw[cc] & 0xFFFF)) < (unsigned)d.W;
-                        cp_async_4z(&Bs[cc * GKR_PITCH + t], ok ? gi + col_off[cc] : I, ok);
+                        cp_async_4z(&Bs[cc * pitch + k], ok ? gim + col_off[cc] : I, ok);
                     } else {
-                        cp_async_4(&Bs[cc * GKR_PITCH + t], gi + col_off[cc]);
+                        cp_async_4(&Bs[cc * pitch + k], gim + col_off[cc]);
                     }
                 }
+            }
+            // pad the chunk to whole rings of the multiplying warps with the identity of the chains
+            for (int q = len + t; q < gkr_padded(len); q += GKR_STAGERS) {
+#pragma unroll
+                for (int row = 0; row < ROWS; row++) As[row * pitch + q] = -0.0f;
+#pragma unroll
+                for (int cc = 0; cc < COLS; cc++) Bs[cc * pitch + q] = 0.0f;
             }
         };
         // operand watch of a landed chunk: every staging thread looks at the elements it copied itself
         auto watch = [&](int st, const GkChunk &c) {
-            const float *As = gkr_smem + st * STAGE, *Bs = As + ROWS * GKR_PITCH;
+            const float *As = gkr_smem + st * STAGE, *Bs = As + ROWS * pitch;
             const int len = chunk_len(c);
             if (a16) {
-#pragma unroll
-                for (int m = 0; m < A16M; m++) {
-                    const int q = 4 * (a16l + LPR * m);
-                    if (q < len) {
-                        const float4 v = *reinterpret_cast<const float4 *>(&As[a16r * GKR_PITCH + q]);
-                        unsafe |= cg_unsafe(v.x) | cg_unsafe(v.y) | cg_unsafe(v.z) | cg_unsafe(v.w);
-                    }
+                for (int q = 4 * a16l; q < len; q += 4 * LPR) {
+                    const float4 v = *reinterpret_cast<const float4 *>(&As[a16r * pitch + q]);
+                    unsafe |= cg_unsafe(v.x) | cg_unsafe(v.y) | cg_unsafe(v.z) | cg_unsafe(v.w);
                 }
             }
-            if (t < len) {
+#pragma unroll 1
+            for (int m = 0; m < GKR_KPT; m++) {
+                const int k = t + m * GKR_STAGERS;
+                if (k >= len) break;
                 if (!a16) {
 #pragma unroll
-                    for (int row = 0; row < ROWS; row++) unsafe |= cg_unsafe(As[row * GKR_PITCH + t]);
+                    for (int row = 0; row < ROWS; row++) unsafe |= cg_unsafe(As[row * pitch + k]);
                 }
 #pragma unroll
-                for (int cc = 0; cc < COLS; cc++) unsafe |= cg_unsafe(Bs[cc * GKR_PITCH + t]);
+                for (int cc = 0; cc < COLS; cc++) unsafe |= cg_unsafe(Bs[cc * pitch + k]);
             }
         };
 
@@ -1237,71 +1262,73 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
         }
         cp_async_wait<0>();
     } else {
-        // Operands are fetched a group of 8 steps ahead into a second register set (the loop's trip
-        // count is not a constant, so the compiler would not move the loads of a later iteration above
-        // the FMAs of an earlier one by itself).  Measured on B200: a warp spends about 4 cycles per
-        // step on the dependent FMA and about 4 more on its two 16-byte shared-memory loads per four
-        // steps, whose passes do not overlap with the warp's own FMAs; longer groups were slower.
-        constexpr int G = 2;  // float4 steps per group
-        auto multiply = [&](int st, int len) {
-            const float4 *ar = reinterpret_cast<const float4 *>(gkr_smem + st * STAGE + crow * GKR_PITCH);
-            const float4 *br =
-                reinterpret_cast<const float4 *>(gkr_smem + st * STAGE + (ROWS + ccol) * GKR_PITCH);
-            const int k4 = len >> 2, ng = k4 / G;
-            float4 aA[G], bA[G], aB[G], bB[G];
-            auto load = [&](float4 (&a)[G], float4 (&b)[G], int g) {
-#pragma unroll
-                for (int i = 0; i < G; i++) a[i] = ar[g * G + i], b[i] = br[g * G + i];
-            };
-            auto fma = [&](const float4 (&a)[G], const float4 (&b)[G]) {
-#pragma unroll
-                for (int i = 0; i < G; i++) {
-                    acc = __fmaf_rn(a[i].x, b[i].x, acc);
-                    acc = __fmaf_rn(a[i].y, b[i].y, acc);
-                    acc = __fmaf_rn(a[i].z, b[i].z, acc);
-                    acc = __fmaf_rn(a[i].w, b[i].w, acc);
-                    if (do_bias) {
-                        accb = __fadd_rn(accb, a[i].x);
-                        accb = __fadd_rn(accb, a[i].y);
-                        accb = __fadd_rn(accb, a[i].z);
-                        accb = __fadd_rn(accb, a[i].w);
-                    }
-                }
-            };
-            if (ng > 0) load(aA, bA, 0);
-            int g = 0;
-            for (; g + 2 <= ng; g += 2) {
-                load(aB, bB, g + 1);
-                fma(aA, bA);
-                if (g + 2 < ng) load(aA, bA, g + 2);
-                fma(aB, bB);
-            }
-            if (g < ng) fma(aA, bA);
-            for (int i = ng * G; i < k4; i++) {
-                const float4 a = ar[i], b = br[i];
+        // A group is 4 steps: one 16-byte load of the row operand, one of the column operand, four
+        // dependent FMAs.  The loads of a group are issued GKR_RING groups (about 100 cycles of FMAs)
+        // before its FMAs, into a ring of register sets whose loop is unrolled so that every set has
+        // fixed registers.  Measured on B200: a 16-byte shared-memory load that the warp has to wait
+        // for costs it far more than the 16 cycles of a group, loads it does not wait for cost
+        // nothing, and so does the separate chain of the bias gradient.  The loop has no branch but
+        // its own: chunks are padded to whole rings by the staging warps (row operand -0, column
+        // operand +0: acc + (-0 * +0) = acc and accb + -0 = accb for every value, -0 included).
+        // The pipeline does not drain between chunks: when the loads of a chunk have all been issued
+        // the warp passes the barrier of the next chunk (loads issued before a barrier have read their
+        // data when it completes, so the staging warps may refill the stage) and loads the first ring
+        // of that chunk while it multiplies the last ring of this one.
+        auto walk = [&](auto with_bias) {
+            constexpr bool WB = decltype(with_bias)::value;
+            auto fma4 = [&](const float4 &a, const float4 &b) {
                 acc = __fmaf_rn(a.x, b.x, acc);
                 acc = __fmaf_rn(a.y, b.y, acc);
                 acc = __fmaf_rn(a.z, b.z, acc);
                 acc = __fmaf_rn(a.w, b.w, acc);
-                if (do_bias) {
+                if (WB) {
                     accb = __fadd_rn(accb, a.x);
                     accb = __fadd_rn(accb, a.y);
                     accb = __fadd_rn(accb, a.z);
                     accb = __fadd_rn(accb, a.w);
                 }
+            };
+            float4 ra[GKR_RING], rb[GKR_RING];
+            const float4 *ar = nullptr, *br = nullptr;
+            auto enter_chunk = [&]() {  // barrier of the next chunk; this thread's operand rows in its stage
+                chunk_barrier();
+                ar = reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + crow * pitch);
+                br = reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + (ROWS + ccol) * pitch);
+            };
+            if (nchunks > 0) {
+                enter_chunk();
+#pragma unroll
+                for (int i = 0; i < GKR_RING; i++) ra[i] = ar[i], rb[i] = br[i];
             }
-            const float *as = reinterpret_cast<const float *>(ar), *bs = reinterpret_cast<const float *>(br);
-            for (int k = 4 * k4; k < len; k++) {
-                acc = __fmaf_rn(as[k], bs[k], acc);
-                if (do_bias) accb = __fadd_rn(accb, as[k]);
+            for (long long ci = 0; ci < nchunks; ci++) {
+                const int ngroups = gkr_padded(chunk_len(cur)) >> 2;  // a multiple of GKR_RING
+                for (int g = GKR_RING; g < ngroups; g += GKR_RING) {
+#pragma unroll
+                    for (int i = 0; i < GKR_RING; i++) {
+                        fma4(ra[i], rb[i]);
+                        ra[i] = ar[g + i], rb[i] = br[g + i];
+                    }
+                }
+                advance(cur);
+                stage = stage + 1 == GKR_STAGES ? 0 : stage + 1;
+                if (ci + 1 < nchunks) {
+                    enter_chunk();
+#pragma unroll
+                    for (int i = 0; i < GKR_RING; i++) {
+                        fma4(ra[i], rb[i]);
+                        ra[i] = ar[i], rb[i] = br[i];
+                    }
+                } else {
+#pragma unroll
+                    for (int i = 0; i < GKR_RING; i++) fma4(ra[i], rb[i]);
+                }
             }
         };
-        for (long long ci = 0; ci < nchunks; ci++) {
-            chunk_barrier();
-            multiply(stage, chunk_len(cur));
-            advance(cur);
-            stage = stage + 1 == GKR_STAGES ? 0 : stage + 1;
-        }
+        // (two copies of the loop: a test of do_bias inside it would cost the chain a branch per group)
+        if (do_bias)
+            walk(std::true_type{});
+        else
+            walk(std::false_type{});
     }
     const bool redo = PADDED ? (__syncthreads_or(unsafe ? 1 : 0) != 0) : false;
     if (!producer) {
@@ -1318,40 +1345,66 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
     }
 }
 
+// Chunk geometry for a tile of `lines` operand rows + columns.  Chunks are as long as three stages
+// of them fit in half of an SM's shared memory (so that two CTAs, of this convolution or of the next
+// layer's, share an SM) and GKR_KMAX allows: every chunk costs the multiplying warps a hand-over, and
+// its padding.  An image is split into equal runs of whole output rows (segW = OW), or, when a row is
+// longer than a chunk, rows into segments.
+struct GkGeom {
+    int segW, R, pitch, smem;
+};
+constexpr int GKR_SMEM_BUDGET = 112 * 1024;
+static GkGeom gk_geometry(const ConvDims &d, int lines)
+{
+    int kmax = GKR_KMAX;
+    while (GKR_STAGES * lines * gkr_pitch(kmax) * (int)sizeof(float) > GKR_SMEM_BUDGET) kmax -= 8;
+    GkGeom g;
+    if (d.OW <= kmax) {
+        const int rows_max = kmax / d.OW < d.OH ? kmax / d.OW : d.OH;
+        const int parts = (d.OH + rows_max - 1) / rows_max;
+        g.segW = d.OW, g.R = (d.OH + parts - 1) / parts;
+        g.pitch = gkr_pitch(g.R * d.OW);
+    } else {
+        g.segW = kmax, g.R = 1;
+        g.pitch = gkr_pitch(kmax);
+    }
+    g.smem = GKR_STAGES * lines * g.pitch * (int)sizeof(float);
+    return g;
+}
+
 template <bool PADDED, int RW, int CB, bool BIAS>
-int launch_gk_rows(const float *go, const float *in, float *gk, float *gb, const ConvDims &d, int segW,
-                   int R, cudaStream_t st)
+int launch_gk_rows(const float *go, const float *in, float *gk, float *gb, const ConvDims &d, cudaStream_t st)
 {
     static unsigned long long done = 0;
     constexpr int ROWS = 4 * RW, COLS = 8 * CB;
-    constexpr int SMEM = GKR_STAGES * (ROWS + COLS) * GKR_PITCH * (int)sizeof(float);
-    int e = ensure_smem(conv_gk_rows_kernel<PADDED, RW, CB, BIAS>, SMEM, &done);
+    const GkGeom g = gk_geometry(d, ROWS + COLS);
+    int e = ensure_smem(conv_gk_rows_kernel<PADDED, RW, CB, BIAS>, GKR_SMEM_BUDGET, &done);
     if (e) return e;
     const int ncols = d.IC * d.KH * d.KW;
-    const long long nchunks = (long long)d.N * ((d.OH + R - 1) / R) * ((d.OW + segW - 1) / segW);
+    const long long nchunks = (long long)d.N * ((d.OH + g.R - 1) / g.R) * ((d.OW + g.segW - 1) / g.segW);
     // 16-byte copies of grad_output need every chunk to start on a 16-byte boundary and to hold a
     // multiple of 4 elements
     const bool a16 = ((uintptr_t)go % 16 == 0) && ((int64_t)d.OH * d.OW % 4 == 0) &&
-                     (segW == d.OW ? ((int64_t)R * d.OW % 4 == 0) : (d.OW % 4 == 0));
+                     (g.segW == d.OW ? ((int64_t)g.R * d.OW % 4 == 0) : (d.OW % 4 == 0));
     dim3 grid((unsigned)((ncols + COLS - 1) / COLS), (unsigned)((d.OC + ROWS - 1) / ROWS));
-    conv_gk_rows_kernel<PADDED, RW, CB, BIAS><<<grid, RW * CB * 32 + GKR_STAGERS, SMEM, st>>>(
-        go, in, gk, gb, d, segW, R, a16 ? 1 : 0, nchunks);
+    conv_gk_rows_kernel<PADDED, RW, CB, BIAS><<<grid, RW * CB * 32 + GKR_STAGERS, g.smem, st>>>(
+        go, in, gk, gb, d, g.segW, g.R, g.pitch, a16 ? 1 : 0, nchunks);
     return launch_status();
 }
 
 // few outputs: patches of 4 x 8 (one multiplying warp per CTA) put them on four times as many SMs
 template <bool BIAS>
-int launch_gk_rows_any(const float *go, const float *in, float *gk, float *gb, const ConvDims &d, int segW,
-                       int R, cudaStream_t st)
+int launch_gk_rows_any(const float *go, const float *in, float *gk, float *gb, const ConvDims &d,
+                       cudaStream_t st)
 {
     const int ncols = d.IC * d.KH * d.KW;
     const bool padded = (d.pH | d.pW) != 0;
     const int64_t big_tiles = (int64_t)((ncols + 15) / 16) * ((d.OC + 7) / 8);
     if (2 * big_tiles < sm_count())
-        return padded ? launch_gk_rows<true, 1, 1, BIAS>(go, in, gk, gb, d, segW, R, st)
-                      : launch_gk_rows<false, 1, 1, BIAS>(go, in, gk, gb, d, segW, R, st);
-    return padded ? launch_gk_rows<true, 2, 2, BIAS>(go, in, gk, gb, d, segW, R, st)
-                  : launch_gk_rows<false, 2, 2, BIAS>(go, in, gk, gb, d, segW, R, st);
+        return padded ? launch_gk_rows<true, 1, 1, BIAS>(go, in, gk, gb, d, st)
+                      : launch_gk_rows<false, 1, 1, BIAS>(go, in, gk, gb, d, st);
+    return padded ? launch_gk_rows<true, 2, 2, BIAS>(go, in, gk, gb, d, st)
+                  : launch_gk_rows<false, 2, 2, BIAS>(go, in, gk, gb, d, st);
 }
 
 int fill_dims(ConvDims &d, int64_t N, int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH,
@@ -1456,22 +1509,14 @@ static int conv2d_grad_kernel_impl(const float *grad_output, const float *input,
         const unsigned gy = (unsigned)((d.OC + GK_ROWS - 1) / GK_ROWS);
         // few outputs: one chain per thread spreads them over twice as many SMs
         const bool narrow = (int64_t)((ncols + 31) / 32) * gy < 2 * (int64_t)sm_count();
-        // chunks of whole output rows (of <= 256 columns of a row when rows are longer)
-        const int segW = d.OW <= GKR_KMAX ? d.OW : GKR_KMAX;
-        int R = d.OW <= GKR_KMAX ? (d.OH < GKR_KMAX / d.OW ? d.OH : GKR_KMAX / d.OW) : 1;
-        // prefer a chunk length that is a whole number of 8-step operand groups, if that costs
-        // less than half the chunk
-        for (int r = R; 2 * r > R; r--)
-            if ((int64_t)r * d.OW % 8 == 0) {
-                R = r;
-                break;
-            }
-        if ((d.OC + 3) / 4 <= 65535 && (int64_t)R * segW >= 64 && d.KH < 32768 && d.KW < 32768 &&
+        // the row-chunk kernel, unless its chunks would be too short to pay for their hand-over
+        const GkGeom g = gk_geometry(d, 12);
+        if ((d.OC + 3) / 4 <= 65535 && (int64_t)g.R * g.segW >= 64 && d.KH < 32768 && d.KW < 32768 &&
             (int64_t)d.OH * d.OW < (1 << 30) && ((int64_t)d.H + 2 * d.pH) * d.W < (1 << 30)) {
-            return grad_bias ? launch_gk_rows_any<true>(grad_output, input, grad_kernel, grad_bias, d, segW,
-                                                        R, (cudaStream_t)stream)
-                             : launch_gk_rows_any<false>(grad_output, input, grad_kernel, nullptr, d, segW,
-                                                         R, (cudaStream_t)stream);
+            return grad_bias ? launch_gk_rows_any<true>(grad_output, input, grad_kernel, grad_bias, d,
+                                                        (cudaStream_t)stream)
+                             : launch_gk_rows_any<false>(grad_output, input, grad_kernel, nullptr, d,
+                                                         (cudaStream_t)stream);
         }
         if (grad_bias) return REPDL_E_UNSUPPORTED;
         if (gy <= 65535 && d.OW < 65536 && (int64_t)d.OH * d.OW < (1 << 24)) {

@@ -1,7 +1,7 @@
 // Elementwise fp32 math for sm_100a: div, sqrt, exp, log with the bits of the reference's CPU run.
 //
-// All four are HBM-bound streams (4 B in, 4 B out per element): 128-bit loads and stores, four
-// independent 16-byte groups in flight per thread, a grid of a few CTAs per SM walking the array
+// All four are HBM-bound streams (4 B in, 4 B out per element): 128-bit loads and stores, three or
+// four independent 16-byte groups in flight per thread, a grid of a few CTAs per SM walking the array
 // with a grid stride.  The arithmetic per element is in crmath.cuh.
 #include "common.cuh"
 #include "crmath.cuh"
@@ -43,6 +43,7 @@ __device__ __forceinline__ void stage_tables(double *sm)
 // needs slow(x)".  The kernels evaluate four elements, OR the flags and branch once.
 struct OpSqrt {
     static constexpr bool kTables = false;
+    static constexpr int kGroups = 3;
     __device__ __forceinline__ float fast(float x, SmemTables, bool &slow) const
     {
         slow = false;
@@ -52,6 +53,7 @@ struct OpSqrt {
 };
 struct OpExp {
     static constexpr bool kTables = true;
+    static constexpr int kGroups = 4;
     __device__ __forceinline__ float fast(float x, SmemTables t, bool &slow) const
     {
         return cr_exp_fast(x, t, slow);
@@ -60,6 +62,7 @@ struct OpExp {
 };
 struct OpLog {
     static constexpr bool kTables = true;
+    static constexpr int kGroups = 3;
     __device__ __forceinline__ float fast(float x, SmemTables t, bool &slow) const
     {
         return cr_log_fast(x, t, slow);
@@ -70,6 +73,7 @@ struct OpLog {
 // subnormal and NaN results).
 struct OpDivScalar {
     static constexpr bool kTables = false;
+    static constexpr int kGroups = 4;
     float d;
     double rd;
     __device__ __forceinline__ float fast(float x, SmemTables, bool &slow) const
@@ -98,37 +102,34 @@ __device__ __forceinline__ float4 apply4(const Op &op, float4 v, SmemTables tab)
 }
 
 constexpr int EW_THREADS = 256;
-constexpr int EW_VEC_PER_THREAD = 4;  // float4 groups in flight per thread per iteration
 
-// (at least four CTAs per SM: log would otherwise take 68 registers and run three; measured 0.72 ->
-// 0.76 of the HBM peak)
+// Op::kGroups 16-byte groups are in flight per thread (measured per operator: three for log and
+// sqrt, four for exp and the division).  At least four CTAs per SM: exp and log would otherwise take
+// 80 registers and run three (exp 0.80 instead of 0.85 of the HBM peak).
 template <class Op>
-#ifndef REPDL_EW_MINB
-#define REPDL_EW_MINB 4
-#endif
-__global__ void __launch_bounds__(EW_THREADS, REPDL_EW_MINB)
+__global__ void __launch_bounds__(EW_THREADS, 4)
 unary_vec_kernel(const float *__restrict__ x, float *__restrict__ y, int64_t nvec, Op op)
 {
     // nvec = number of float4 groups; x and y are 16-byte aligned
     __shared__ __align__(16) double tables[Op::kTables ? TABLE_DOUBLES : 2];
     if (Op::kTables) stage_tables(tables);
     const SmemTables tab{tables};
-    const int64_t stride = (int64_t)gridDim.x * EW_THREADS * EW_VEC_PER_THREAD;
-    for (int64_t base = (int64_t)blockIdx.x * EW_THREADS * EW_VEC_PER_THREAD + threadIdx.x;
-         base < nvec; base += stride) {
-        float4 v[EW_VEC_PER_THREAD];
+    const int64_t stride = (int64_t)gridDim.x * EW_THREADS * Op::kGroups;
+    int64_t base = (int64_t)blockIdx.x * EW_THREADS * Op::kGroups + threadIdx.x;
+    // whole blocks of Op::kGroups groups per thread: no bounds tests
+    for (; base + (Op::kGroups - 1) * EW_THREADS < nvec; base += stride) {
+        float4 v[Op::kGroups];
 #pragma unroll
-        for (int u = 0; u < EW_VEC_PER_THREAD; u++) {
-            int64_t i = base + (int64_t)u * EW_THREADS;
-            if (i < nvec) v[u] = ldg_stream_f4(x + 4 * i);
-        }
+        for (int u = 0; u < Op::kGroups; u++) v[u] = ldg_stream_f4(x + 4 * (base + u * EW_THREADS));
 #pragma unroll
-        for (int u = 0; u < EW_VEC_PER_THREAD; u++) {
-            int64_t i = base + (int64_t)u * EW_THREADS;
-            if (i < nvec) {
-                stg_stream_f4(y + 4 * i, apply4(op, v[u], tab));
-            }
-        }
+        for (int u = 0; u < Op::kGroups; u++)
+            stg_stream_f4(y + 4 * (base + u * EW_THREADS), apply4(op, v[u], tab));
+    }
+    // the ragged end of the array (at most one pass per thread)
+#pragma unroll 1
+    for (int u = 0; u < Op::kGroups; u++) {
+        const int64_t i = base + (int64_t)u * EW_THREADS;
+        if (i < nvec) stg_stream_f4(y + 4 * i, apply4(op, ldg_stream_f4(x + 4 * i), tab));
     }
 }
 
@@ -178,7 +179,7 @@ int launch_unary(const float *x, float *y, int64_t n, Op op, void *stream)
     if (aligned16(x) && aligned16(y)) {
         int64_t nvec = n / 4;
         if (nvec > 0) {
-            unary_vec_kernel<Op><<<grid_for(nvec, EW_THREADS * EW_VEC_PER_THREAD), EW_THREADS, 0,
+            unary_vec_kernel<Op><<<grid_for(nvec, EW_THREADS * Op::kGroups), EW_THREADS, 0,
                                    st>>>(x, y, nvec, op);
             int e = launch_status();
             if (e) return e;
