@@ -29,6 +29,10 @@ static inline bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t
 // Number of SMs of the current device (cached per thread; 148 on B200).
 int sm_count();
 
+// conv.cu: C[m][n] = chain over k of A[m][k] * B[n][k] for dense, k-contiguous operands, on the chain kernel
+// of conv2d_grad_kernel (REPDL_E_UNSUPPORTED when the shape does not suit it).
+int mm_long_k(const float *A, const float *B, float *C, int M, int N, int K, cudaStream_t st);
+
 // The plain single-thread chain walk of sum1d.cu for short chains (no scratch): out[0] = factor * chain.
 int sum1d_plain(const float *x, float *out, int64_t n, float factor, cudaStream_t st);
 

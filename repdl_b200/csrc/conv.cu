@@ -1495,7 +1495,7 @@ extern "C" int repdl_b200_conv2d_grad_input(const float *grad_output, const floa
 static int conv2d_grad_kernel_impl(const float *grad_output, const float *input, float *grad_kernel,
                                    float *grad_bias, int64_t N, int64_t IC, int64_t H, int64_t W,
                                    int64_t OC, int64_t KH, int64_t KW, int64_t sH, int64_t sW, int64_t pH,
-                                   int64_t pW, void *stream)
+                                   int64_t pW, void *stream, bool rows_only = false)
 {
     clear_stale_error();
     ConvDims d;
@@ -1518,7 +1518,7 @@ static int conv2d_grad_kernel_impl(const float *grad_output, const float *input,
                              : launch_gk_rows_any<false>(grad_output, input, grad_kernel, nullptr, d,
                                                          (cudaStream_t)stream);
         }
-        if (grad_bias) return REPDL_E_UNSUPPORTED;
+        if (grad_bias || rows_only) return REPDL_E_UNSUPPORTED;
         if (gy <= 65535 && d.OW < 65536 && (int64_t)d.OH * d.OW < (1 << 24)) {
             if (narrow)
                 conv_gk_kernel<16><<<dim3((unsigned)((ncols + 15) / 16), gy), GK_THREADS, 0,
@@ -1529,13 +1529,21 @@ static int conv2d_grad_kernel_impl(const float *grad_output, const float *input,
             return launch_status();
         }
     }
-    if (grad_bias) return REPDL_E_UNSUPPORTED;
+    if (grad_bias || rows_only) return REPDL_E_UNSUPPORTED;
     unsigned blocks;
     if ((e = blocks_for(total, blocks))) return e;
     conv2d_grad_kernel_direct_kernel<<<blocks, CONV_THREADS, 0, (cudaStream_t)stream>>>(
         grad_output, input, grad_kernel, d, total);
     return launch_status();
 }
+
+namespace repdl_b200 {
+int mm_long_k(const float *A, const float *B, float *C, int M, int N, int K, cudaStream_t st)
+{
+    // grad_output = A as [1, M, 1, K], input = B as [1, N, 1, K], kernel 1 x 1: grad_kernel[m][n]
+    return conv2d_grad_kernel_impl(A, B, C, nullptr, 1, N, 1, K, M, 1, 1, 1, 1, 0, 0, (void *)st, true);
+}
+}  // namespace repdl_b200
 
 extern "C" int repdl_b200_conv2d_grad_kernel(const float *grad_output, const float *input,
                                              float *grad_kernel, int64_t N, int64_t IC, int64_t H,

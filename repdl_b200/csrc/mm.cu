@@ -278,8 +278,9 @@ int launch_shape(const float *A, const float *B, const OutSet &C, int M, int N, 
     const int64_t wide = (int64_t)((M + 63) / 64) * ((N + 127) / 128);
     if (4 * wide >= 3 * sms)
         return launch_one<64, 128, 8, 8, A_KC, B_KC, VEC, 2>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
-    // Few outputs but a long K (e.g. a 256 x 128 layer output over K = 9216): the time is K times
-    // the instructions one warp issues per k-step, so spread the outputs over more, thinner CTAs.
+    // Few outputs but a long K in a layout that the chain kernel (mm_long_k) does not take: the time
+    // is K times the instructions one warp issues per k-step, so spread the outputs over more, thinner
+    // CTAs.
     const int64_t small = (int64_t)((M + 63) / 64) * ((N + 63) / 64);
     if (small * 4 <= sms && K >= 1024)
         return launch_one<32, 32, 4, 4, A_KC, B_KC, VEC, 8, 4>(A, B, C, M, N, K, lda, ldb, ldc, vecC, st);
@@ -330,6 +331,16 @@ static int mm_dispatch(const float *A, const float *B, const OutSet &out, int64_
     int vecC = ldc % 4 == 0 && N % 4 == 0;
     for (int r = 0; r < out.n; r++) vecC = vecC && aligned16(out.p[r]);
     const int m = (int)M, n = (int)N, k = (int)K;
+    // Few outputs over a long K with both operands k-contiguous and dense (a layer's forward product
+    // x W^T): one chain per thread on the chain kernel of the convolution weight gradient, which this
+    // product is (C[m][n] = sum_k A[m][k] B[n][k] is the gradient of a 1 x 1 kernel over one image of
+    // 1 x K pixels).  256 x 128 outputs over K = 9216: 0.2 ms on 32 x 32 tiles here, because 64 warps
+    // issue all the FMAs.
+    if (a_kc && b_kc && out.n == 1 && lda == K && ldb == K && ldc == N && K >= 2048 && K % 4 == 0 &&
+        aligned16(A) && (int64_t)((M + 63) / 64) * ((N + 63) / 64) * 4 <= sm_count()) {
+        const int e = mm_long_k(A, B, out.p[0], m, n, k, st);
+        if (e != REPDL_E_UNSUPPORTED) return e;
+    }
 #define REPDL_MM_CASE(AKC, BKC)                                                              \
     (vec ? launch_shape<AKC, BKC, true>(A, B, out, m, n, k, lda, ldb, ldc, vecC, st)         \
          : launch_shape<AKC, BKC, false>(A, B, out, m, n, k, lda, ldb, ldc, vecC, st))

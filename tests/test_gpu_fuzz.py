@@ -157,6 +157,23 @@ def test_mm_random_shapes(shape):
     assert bits_equal(ops.mm(a.cuda(), b.cuda(), ta, tb), oracle.mm(a, b, ta, tb))
 
 
+@pytest.mark.parametrize("shape", [(256, 128, 9216), (37, 50, 2048), (5, 3, 4100), (64, 64, 2060), (1, 1, 2048),
+                                   (130, 9, 3000)])
+def test_mm_few_outputs_over_a_long_k(shape):
+    """x W^T with few outputs and a long K runs on the chain kernel of the convolution weight gradient
+    (one chain per thread, chunks padded with the chain's identity): same bits as the tiled kernel's."""
+    from repdl_b200 import ops
+    M, N, K = shape
+    g = torch.Generator().manual_seed(M * 7919 + N * 104729 + K)
+    a, b = _randn(g, M, K), _randn(g, N, K)
+    a[0, : K // 2] = -1e-30  # products that underflow to -0 keep the accumulator at -0 through the padding
+    b[0, : K // 2] = 1e-30
+    a[0, K // 2:] = 0.0
+    assert bits_equal(ops.mm(a.cuda(), b.cuda(), False, True), oracle.mm(a, b, False, True))
+    # the same operands in the other layouts take the tiled kernel
+    assert bits_equal(ops.mm(a.cuda(), b.t().contiguous().cuda(), False, False), oracle.mm(a, b, False, True))
+
+
 def test_chain_sums_random_shapes():
     from repdl_b200 import ops
     rnd = random.Random(5)
