@@ -1106,13 +1106,17 @@ struct GkChunk {
 };
 
 // RW x CB multiplying warps, each owning a patch of 4 output channels x 8 weight columns.
-// BIAS: the CTAs of the first column block also add up their rows of grad_output -- the row operand
-// the chains consume anyway, in the order n, oh, ow of the reference's sum4d_dim023 -- and write the
-// bias gradient, which saves the separate pass over grad_output.
+// BIAS: the kernel also adds up the rows of grad_output in the order n, oh, ow of the reference's
+// sum4d_dim023 and writes the bias gradient, which saves a separate pass over grad_output.  A bias
+// chain is as long as a weight chain.  Where the grid leaves SMs free (bias_sep), one more column
+// block of CTAs carries the bias chains alone: those CTAs stage and read the row operand only.
+// Otherwise the threads of the first column block carry a second chain, which costs them 0.5 to 0.9
+// cycles per step (but a CTA that has to share its SM costs the kernel far more).
 template <bool PADDED, int RW, int CB, bool BIAS>
 __global__ void __launch_bounds__((RW * CB) * 32 + GKR_STAGERS, 2)
 conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, float *__restrict__ GK,
-                    float *__restrict__ GB, ConvDims d, int segW, int R, int pitch, int a16, long long nchunks)
+                    float *__restrict__ GB, ConvDims d, int segW, int R, int pitch, int a16, int bias_sep,
+                    long long nchunks)
 {
     extern __shared__ __align__(16) float gkr_smem[];
     constexpr int ROWS = 4 * RW, COLS = 8 * CB, NCW = RW * CB;
@@ -1143,7 +1147,8 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
     int stage = 0;  // stage of chunk ci; the chunk issued in iteration ci goes to the stage before it
     bool unsafe = false;
     float acc = 0.0f, accb = 0.0f;
-    const bool do_bias = BIAS && blockIdx.x == 0;
+    const bool bias_only = BIAS && bias_sep && blockIdx.x == gridDim.x - 1;  // this CTA only adds up rows
+    const bool bias_too = BIAS && !bias_sep && blockIdx.x == 0;              // second chain per thread
     // Multiplying role: which output of the CTA's tile a thread owns.  Shared memory serves a 16-byte
     // load eight lanes at a time, and passes of one load that fetch the same addresses in the same
     // lanes are merged.  So the lanes of a warp's 4 x 8 patch are laid out with all four rows in
@@ -1199,6 +1204,7 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
                         cp_async_4(&As[row * pitch + k], ga + (int64_t)rr * OHW + k);
                     }
                 }
+                if (bias_only) continue;
                 const float *gim = gi + boff[m];
                 const int hj = c.oh0 * d.sH + hb[m], wj = c.ow0 * d.sW + wb[m];
 #pragma unroll
@@ -1216,6 +1222,7 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
             for (int q = len + t; q < gkr_padded(len); q += GKR_STAGERS) {
 #pragma unroll
                 for (int row = 0; row < ROWS; row++) As[row * pitch + q] = -0.0f;
+                if (bias_only) continue;
 #pragma unroll
                 for (int cc = 0; cc < COLS; cc++) Bs[cc * pitch + q] = 0.0f;
             }
@@ -1238,6 +1245,7 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
 #pragma unroll
                     for (int row = 0; row < ROWS; row++) unsafe |= cg_unsafe(As[row * pitch + k]);
                 }
+                if (bias_only) continue;
 #pragma unroll
                 for (int cc = 0; cc < COLS; cc++) unsafe |= cg_unsafe(Bs[cc * pitch + k]);
             }
@@ -1267,21 +1275,25 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
         // before its FMAs, into a ring of register sets whose loop is unrolled so that every set has
         // fixed registers.  Measured on B200: a 16-byte shared-memory load that the warp has to wait
         // for costs it far more than the 16 cycles of a group, loads it does not wait for cost
-        // nothing, and so does the separate chain of the bias gradient.  The loop has no branch but
-        // its own: chunks are padded to whole rings by the staging warps (row operand -0, column
-        // operand +0: acc + (-0 * +0) = acc and accb + -0 = accb for every value, -0 included).
+        // nothing (4.4 cycles per step for the whole loop), a second dependent chain in the same
+        // thread costs 0.5 to 0.9 cycles per step.  The loop has no branch but its own: chunks are
+        // padded to whole rings by the staging warps (row operand -0, column operand +0:
+        // acc + (-0 * +0) = acc and accb + -0 = accb for every value, -0 included).
         // The pipeline does not drain between chunks: when the loads of a chunk have all been issued
         // the warp passes the barrier of the next chunk (loads issued before a barrier have read their
         // data when it completes, so the staging warps may refill the stage) and loads the first ring
         // of that chunk while it multiplies the last ring of this one.
-        auto walk = [&](auto with_bias) {
-            constexpr bool WB = decltype(with_bias)::value;
-            auto fma4 = [&](const float4 &a, const float4 &b) {
-                acc = __fmaf_rn(a.x, b.x, acc);
-                acc = __fmaf_rn(a.y, b.y, acc);
-                acc = __fmaf_rn(a.z, b.z, acc);
-                acc = __fmaf_rn(a.w, b.w, acc);
-                if (WB) {
+        auto walk = [&](auto mode) {
+            constexpr int MODE = decltype(mode)::value;  // 0: multiply, 1: multiply and add up rows, 2: add up rows
+            constexpr bool BO = MODE == 2;
+            auto step4 = [&](const float4 &a, const float4 &b) {
+                if (MODE != 2) {
+                    acc = __fmaf_rn(a.x, b.x, acc);
+                    acc = __fmaf_rn(a.y, b.y, acc);
+                    acc = __fmaf_rn(a.z, b.z, acc);
+                    acc = __fmaf_rn(a.w, b.w, acc);
+                }
+                if (MODE != 0) {
                     accb = __fadd_rn(accb, a.x);
                     accb = __fadd_rn(accb, a.y);
                     accb = __fadd_rn(accb, a.z);
@@ -1295,18 +1307,22 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
                 ar = reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + crow * pitch);
                 br = reinterpret_cast<const float4 *>(gkr_smem + stage * STAGE + (ROWS + ccol) * pitch);
             };
+            auto load = [&](int i, int g) {
+                ra[i] = ar[g];
+                if (!BO) rb[i] = br[g];
+            };
             if (nchunks > 0) {
                 enter_chunk();
 #pragma unroll
-                for (int i = 0; i < GKR_RING; i++) ra[i] = ar[i], rb[i] = br[i];
+                for (int i = 0; i < GKR_RING; i++) load(i, i);
             }
             for (long long ci = 0; ci < nchunks; ci++) {
                 const int ngroups = gkr_padded(chunk_len(cur)) >> 2;  // a multiple of GKR_RING
                 for (int g = GKR_RING; g < ngroups; g += GKR_RING) {
 #pragma unroll
                     for (int i = 0; i < GKR_RING; i++) {
-                        fma4(ra[i], rb[i]);
-                        ra[i] = ar[g + i], rb[i] = br[g + i];
+                        step4(ra[i], rb[i]);
+                        load(i, g + i);
                     }
                 }
                 advance(cur);
@@ -1315,25 +1331,28 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
                     enter_chunk();
 #pragma unroll
                     for (int i = 0; i < GKR_RING; i++) {
-                        fma4(ra[i], rb[i]);
-                        ra[i] = ar[i], rb[i] = br[i];
+                        step4(ra[i], rb[i]);
+                        load(i, i);
                     }
                 } else {
 #pragma unroll
-                    for (int i = 0; i < GKR_RING; i++) fma4(ra[i], rb[i]);
+                    for (int i = 0; i < GKR_RING; i++) step4(ra[i], rb[i]);
                 }
             }
         };
-        // (two copies of the loop: a test of do_bias inside it would cost the chain a branch per group)
-        if (do_bias)
-            walk(std::true_type{});
+        // (a copy of the loop per mode: a test inside it would cost the chain a branch per group)
+        if (bias_only)
+            walk(std::integral_constant<int, 2>{});
+        else if (bias_too)
+            walk(std::integral_constant<int, 1>{});
         else
-            walk(std::false_type{});
+            walk(std::integral_constant<int, 0>{});
     }
     const bool redo = PADDED ? (__syncthreads_or(unsafe ? 1 : 0) != 0) : false;
     if (!producer) {
         const int oc = oc0 + crow, col = col0 + ccol;
-        if (oc < d.OC && col < ncols) {
+        if ((bias_only || bias_too) && ccol == 0 && oc < d.OC) GB[oc] = accb;
+        if (!bias_only && oc < d.OC && col < ncols) {
             float v = acc;
             if (redo) {
                 const int ic = col / KHW, r = col - ic * KHW;
@@ -1341,7 +1360,6 @@ conv_gk_rows_kernel(const float *__restrict__ GO, const float *__restrict__ I, f
             }
             GK[(int64_t)oc * ncols + col] = v;
         }
-        if (do_bias && ccol == 0 && oc < d.OC) GB[oc] = accb;
     }
 }
 
@@ -1387,8 +1405,11 @@ int launch_gk_rows(const float *go, const float *in, float *gk, float *gb, const
     const bool a16 = ((uintptr_t)go % 16 == 0) && ((int64_t)d.OH * d.OW % 4 == 0) &&
                      (g.segW == d.OW ? ((int64_t)g.R * d.OW % 4 == 0) : (d.OW % 4 == 0));
     dim3 grid((unsigned)((ncols + COLS - 1) / COLS), (unsigned)((d.OC + ROWS - 1) / ROWS));
+    // the bias chains in CTAs of their own if every CTA then still has an SM to itself
+    const bool bias_sep = BIAS && (int64_t)(grid.x + 1) * grid.y <= sm_count();
+    if (bias_sep) grid.x++;
     conv_gk_rows_kernel<PADDED, RW, CB, BIAS><<<grid, RW * CB * 32 + GKR_STAGERS, g.smem, st>>>(
-        go, in, gk, gb, d, g.segW, g.R, g.pitch, a16 ? 1 : 0, nchunks);
+        go, in, gk, gb, d, g.segW, g.R, g.pitch, a16 ? 1 : 0, bias_sep ? 1 : 0, nchunks);
     return launch_status();
 }
 
