@@ -742,6 +742,8 @@ def main():
         if rank == 0:
             h = hashlib.sha256(sh.C.cpu().numpy().tobytes()).hexdigest()
             ok = h == gold["sha256"] and mine_ok == 1
+            if e2e is not None and world == 1:  # what the host-operand step brought back to the host
+                ok = ok and hashlib.sha256(c_host.numpy().tobytes()).hexdigest() == gold["sha256"]
             parity = ("sha256 equal to reference CPU backend" + (
                 "; every rank's own row blocks too" if world > 1 and Mp % 2048 == 0 else "")) if ok else "MISMATCH"
 

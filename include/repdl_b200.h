@@ -42,6 +42,14 @@ int repdl_b200_sm_arch(void);
 /* Human-readable text for a status returned by any call below (static storage). */
 const char *repdl_b200_strerror(int status);
 
+/* Strided sub-matrix copy on a stream: `rows` rows of `width_bytes` bytes, source and destination
+ * with their own row pitches.  direction 0: host -> device, 1: device -> host, 2: device -> device.
+ * No counterpart in the reference (its operators take whole tensors that live on the device): the
+ * host-operand step of repdl_b200.dist uploads B by column blocks with it, so that the first product
+ * can start before all of B has arrived.  Host memory should be pinned. */
+int repdl_b200_copy2d(void *dst, int64_t dst_pitch_bytes, const void *src, int64_t src_pitch_bytes,
+                      int64_t width_bytes, int64_t rows, int direction, void *stream);
+
 /* ---- matrix multiplication -------------------------------------------------------------
  * Replaces repdl::cuda::matrix_multiplication::mm (backend/cuda/matrix_multiplication.cu:234-260),
  * bits defined by backend/cpu/matrix_multiplication.cpp:12-36:

@@ -22,3 +22,23 @@ extern "C" const char *repdl_b200_strerror(int status)
     if (status > 0) return cudaGetErrorString((cudaError_t)status);
     return "unknown repdl_b200 status";
 }
+
+// Strided sub-matrix copy on a stream (cudaMemcpy2DAsync): `rows` rows of `width_bytes` bytes each.
+// direction 0: host -> device, 1: device -> host, 2: device -> device.  Host memory should be pinned,
+// or the copy is not asynchronous.
+extern "C" int repdl_b200_copy2d(void *dst, int64_t dst_pitch_bytes, const void *src, int64_t src_pitch_bytes,
+                                 int64_t width_bytes, int64_t rows, int direction, void *stream)
+{
+    repdl_b200::clear_stale_error();
+    if (width_bytes < 0 || rows < 0 || dst_pitch_bytes < width_bytes || src_pitch_bytes < width_bytes)
+        return REPDL_E_SHAPE;
+    if (width_bytes == 0 || rows == 0) return REPDL_OK;
+    if (!dst || !src) return REPDL_E_NULL;
+    const cudaMemcpyKind kind = direction == 0   ? cudaMemcpyHostToDevice
+                                : direction == 1 ? cudaMemcpyDeviceToHost
+                                : direction == 2 ? cudaMemcpyDeviceToDevice
+                                                 : cudaMemcpyDefault;
+    if (direction < 0 || direction > 2) return REPDL_E_UNSUPPORTED;
+    return (int)cudaMemcpy2DAsync(dst, (size_t)dst_pitch_bytes, src, (size_t)src_pitch_bytes, (size_t)width_bytes,
+                                  (size_t)rows, kind, (cudaStream_t)stream);
+}

@@ -179,15 +179,69 @@ def _side_streams(device):
     return _copy_streams[key]
 
 
+def _dense2d(*tensors):
+    return all(t.dim() == 2 and t.stride(1) == 1 and t.stride(0) >= t.shape[1] for t in tensors)
+
+
+def _copy_cols_h2d(dst, src, c0, c1, stream):
+    """Columns [c0, c1) of a pinned host matrix to the same columns of a device matrix, on `stream`."""
+    from ._cabi import check, lib
+    check(lib.repdl_b200_copy2d(dst.data_ptr() + 4 * c0, 4 * dst.stride(0), src.data_ptr() + 4 * c0,
+                                4 * src.stride(0), 4 * (c1 - c0), dst.shape[0], 0, stream.cuda_stream), "copy2d")
+
+
+def _equal_blocks(rows, chunks):
+    step = -(-rows // chunks)
+    return [(r0, min(rows, r0 + step)) for r0 in range(0, rows, step)]
+
+
+def _row_blocks(rows, n_cols, chunks, sms):
+    """Row blocks [(r0, r1), ...] for the pipelined host-operand step.
+
+    Equal blocks waste the last wave of every launch (2048 rows of 16384 columns are 6.9 waves of
+    192 x 128 tiles on 148 SMs: 4 % lost eight times).  So block heights are chosen in units of the
+    192-row tile to fill whole waves, with a smaller first block (its upload is not hidden) and a
+    smaller last block (its download is not hidden).  Small problems keep equal blocks."""
+    unit = 192
+    units = -(-rows // unit)   # the last unit may be partial
+    if units < 4 * chunks:
+        return _equal_blocks(rows, chunks)
+    tiles_per_unit = -(-n_cols // 128)
+    waves = lambda r: -(-r * tiles_per_unit // sms)                      # launches of r units
+    loss = lambda r: waves(r) - r * tiles_per_unit / sms                  # idle fraction of its last wave
+    target = units / chunks
+    edge = min(range(max(1, int(0.3 * target)), max(2, int(0.9 * target)) + 1), key=lambda r: (loss(r) / r, r))
+    inner_sizes = sorted(range(max(1, int(0.7 * target)), int(1.6 * target) + 1), key=lambda r: (loss(r) / r, -r))
+    best = None
+    for mid in inner_sizes[:4]:
+        left = units - 2 * edge
+        if left < 0:
+            continue
+        n_mid, rest = divmod(left, mid)
+        sizes = [edge] + [mid] * n_mid + ([rest] if rest else []) + [edge]
+        cost = sum(waves(r) for r in sizes) + 0.5 * len(sizes)
+        if best is None or cost < best[0]:
+            best = (cost, sizes)
+    if best is None:
+        return _equal_blocks(rows, chunks)
+    out, r0 = [], 0
+    for r in best[1]:
+        out.append((r0 * unit, min(rows, (r0 + r) * unit)))
+        r0 += r
+    return out
+
+
 def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chunks=8):
     """End-to-end step with HOST operands: pinned A panel and B go to the device, the sharded
     product runs, and this rank's panel of C comes back to pinned host memory.
 
-    One GPU: the step is a pipeline over `chunks` row blocks of A.  B and the blocks of A are uploaded
-    in that order on a copy stream, block i is multiplied as soon as it has arrived, and its rows of C
-    go back on a second copy stream while block i + 1 is multiplied, so after B only the first upload
-    and the last download are exposed.  (Rows of C are independent chains, so the bits are those of
-    the one-launch product.)
+    One GPU: the step is a pipeline over about `chunks` row blocks of A (heights that fill whole waves
+    of the product's tiles, see _row_blocks).  The first block of A goes up first, then B in four
+    column parts, each multiplied with that block as soon as it has arrived, then the other blocks of
+    A; block i is multiplied when it is there, and its rows of C go back on a second copy stream
+    while block i + 1 is multiplied.  What stays exposed is the first block of A, a quarter of B and
+    the last download.  (Every element of C is its own chain over the whole of K, so the bits are
+    those of the one-launch product.)
 
     Several GPUs: every rank has the same B in host memory, so each uploads only its 1/world of B's
     rows and the ranks all-gather B over NVLink -- world times less PCIe traffic for B than uploading
@@ -224,7 +278,7 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chun
         c_host_panel.copy_(sharded.my_rows(), non_blocking=True)
         return C
     rows = a_dev.shape[0]
-    if dev.type != "cuda" or chunks <= 1 or rows % chunks or rows // chunks < 256:
+    if dev.type != "cuda" or chunks <= 1 or rows // chunks < 256:
         a_dev.copy_(a_host_panel, non_blocking=True)
         b_dev.copy_(b_host, non_blocking=True)
         C = sharded(a_dev, b_dev)
@@ -232,26 +286,45 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chun
         return C
     cur = torch.cuda.current_stream(dev)
     up, down = _side_streams(dev)
-    step = rows // chunks
+    N = b_dev.shape[1]
+    blocks = _row_blocks(rows, N, chunks, torch.cuda.get_device_properties(dev).multi_processor_count)
+    # the first block's product runs by column parts of B, each as soon as it has arrived
+    parts = 4 if N % 2048 == 0 and _dense2d(b_dev, b_host) else 1
     up.wait_stream(cur)      # the buffers may still be in use by what the caller queued before
     down.wait_stream(cur)
-    arrived = []
+    a_there, b_there = [], []
     with torch.cuda.stream(up):
-        b_dev.copy_(b_host, non_blocking=True)
-        for i in range(chunks):
-            a_dev[i * step:(i + 1) * step].copy_(a_host_panel[i * step:(i + 1) * step], non_blocking=True)
+        for i, (r0, r1) in enumerate(blocks):
+            a_dev[r0:r1].copy_(a_host_panel[r0:r1], non_blocking=True)
             ev = torch.cuda.Event()
             ev.record(up)
-            arrived.append(ev)
+            a_there.append(ev)
+            if i == 0:
+                w = N // parts
+                for j in range(parts):
+                    if parts == 1:
+                        b_dev.copy_(b_host, non_blocking=True)
+                    else:
+                        _copy_cols_h2d(b_dev, b_host, j * w, (j + 1) * w, up)
+                    ev = torch.cuda.Event()
+                    ev.record(up)
+                    b_there.append(ev)
     C = sharded.C
-    for i in range(chunks):
-        cur.wait_event(arrived[i])
-        sharded.mm_into(a_dev[i * step:(i + 1) * step], b_dev, C[i * step:(i + 1) * step])
-        sharded.kernel_launches += 1
+    for i, (r0, r1) in enumerate(blocks):
+        cur.wait_event(a_there[i])
+        if i == 0:
+            w = N // parts
+            for j in range(parts):
+                cur.wait_event(b_there[j])
+                sharded.mm_into(a_dev[r0:r1], b_dev[:, j * w:(j + 1) * w], C[r0:r1, j * w:(j + 1) * w])
+                sharded.kernel_launches += 1
+        else:
+            sharded.mm_into(a_dev[r0:r1], b_dev, C[r0:r1])
+            sharded.kernel_launches += 1
         done = torch.cuda.Event()
         done.record(cur)
         down.wait_event(done)
         with torch.cuda.stream(down):
-            c_host_panel[i * step:(i + 1) * step].copy_(C[i * step:(i + 1) * step], non_blocking=True)
+            c_host_panel[r0:r1].copy_(C[r0:r1], non_blocking=True)
     cur.wait_stream(down)    # the caller's stream order covers the whole step
     return C

@@ -208,6 +208,33 @@ def test_mm_from_host_pipeline_equals_one_launch(ops):
         assert torch.equal(c_host.view(torch.int32), want.cpu().view(torch.int32))
 
 
+def test_mm_from_host_wave_aligned_blocks_and_column_parts(ops):
+    """A problem large enough for the unequal, wave-aligned row blocks, with B uploaded by column parts
+    (strided copies) and the first block multiplied part by part: bits of the one-launch product."""
+    from repdl_b200.dist import ShardedMM, mm_from_host, _row_blocks
+    M, N, K = 6150, 2048, 72
+    blocks = _row_blocks(M, N, 8, torch.cuda.get_device_properties(0).multi_processor_count)
+    assert blocks[0][0] == 0 and blocks[-1][1] == M and all(a[1] == b[0] for a, b in zip(blocks, blocks[1:]))
+    assert len({r1 - r0 for r0, r1 in blocks}) > 1  # not the equal split
+    g = torch.Generator().manual_seed(78)
+    a = (torch.rand(M, K, generator=g) * 2 - 1)
+    b = (torch.rand(K, N, generator=g) * 2 - 1)
+    want = ops.mm(a.cuda(), b.cuda())
+    sh = ShardedMM(M, N, K, device="cuda")
+    a_host, b_host = a.pin_memory(), b.pin_memory()
+    a_dev, b_dev = torch.zeros(M, K, device="cuda"), torch.zeros(K, N, device="cuda")
+    c_host = torch.zeros(M, N).pin_memory()
+    for rep in range(2):
+        sh.C.zero_(), b_dev.zero_(), c_host.zero_()
+        sh.kernel_launches = 0
+        c = mm_from_host(sh, a_host, b_host, a_dev, b_dev, c_host, chunks=8)
+        torch.cuda.synchronize()
+        assert sh.kernel_launches == len(blocks) + 3
+        assert torch.equal(b_dev.cpu(), b)
+        assert torch.equal(c.view(torch.int32), want.view(torch.int32))
+        assert torch.equal(c_host.view(torch.int32), want.cpu().view(torch.int32))
+
+
 def test_config3_full_chain_and_rows(ops):
     """Config 3 at full size: the 2^30-element chain (checked against the reference's running
     state after every quarter and at the end) and the [65536, 4096] row sums."""
