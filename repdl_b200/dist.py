@@ -237,7 +237,7 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chun
 
     One GPU: the step is a pipeline over about `chunks` row blocks of A (heights that fill whole waves
     of the product's tiles, see _row_blocks).  The first block of A goes up first, then B in four
-    column parts, each multiplied with that block as soon as it has arrived, then the other blocks of
+    or eight column parts, each multiplied with that block as soon as it has arrived, then the other blocks of
     A; block i is multiplied when it is there, and its rows of C go back on a second copy stream
     while block i + 1 is multiplied.  What stays exposed is the first block of A, a quarter of B and
     the last download.  (Every element of C is its own chain over the whole of K, so the bits are
@@ -289,7 +289,7 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chun
     N = b_dev.shape[1]
     blocks = _row_blocks(rows, N, chunks, torch.cuda.get_device_properties(dev).multi_processor_count)
     # the first block's product runs by column parts of B, each as soon as it has arrived
-    parts = 4 if N % 2048 == 0 and _dense2d(b_dev, b_host) else 1
+    parts = (8 if N % 4096 == 0 else 4) if N % 2048 == 0 and _dense2d(b_dev, b_host) else 1
     up.wait_stream(cur)      # the buffers may still be in use by what the caller queued before
     down.wait_stream(cur)
     a_there, b_there = [], []
