@@ -103,6 +103,35 @@ class ShardedMM:
         # collective has: it is ordered after the kernel on each rank's stream
         dist.all_reduce(self._flag, group=self.group)
 
+    # -- the product, block by block (for callers that pipeline it with copies) ---------------------
+    def begin_step(self):
+        """Before the first rows_into_all() of a step: in p2p mode no peer may store into this rank's
+        C before this rank has finished with the previous result."""
+        if self.mode == "p2p":
+            dist.all_reduce(self._flag, group=self.group)
+
+    def rows_into_all(self, a_rows, b, r0):
+        """The product of rows [r0, r0 + len(a_rows)) of this rank's panel: into every rank's C in
+        p2p mode, into this rank's C otherwise (end_step() then gathers)."""
+        if self.mode == "p2p":
+            from ._cabi import check, lib
+            st = torch.cuda.current_stream(self.device).cuda_stream
+            check(lib.repdl_b200_mm_allgather(a_rows.data_ptr(), b.data_ptr(), self._peer_ptrs, self.world,
+                                              self.row0 + r0, a_rows.shape[0], self.N, self.K, 0, 0,
+                                              a_rows.stride(0), b.stride(0), self.C.stride(0), st),
+                  "mm_allgather")
+        else:
+            self.mm_into(a_rows, b, self.my_rows()[r0:r0 + a_rows.shape[0]])
+        self.kernel_launches += 1
+
+    def end_step(self):
+        """After the last rows_into_all() of a step: the whole of C is on every rank when the stream
+        has passed this point."""
+        if self.mode == "p2p":
+            dist.all_reduce(self._flag, group=self.group)
+        elif self.world > 1:
+            dist.all_gather_into_tensor(self.C, self.my_rows(), group=self.group)
+
     # -- the product -----------------------------------------------------------------------------
     def __call__(self, a_panel, b):
         """a_panel: this rank's [M/world, K] rows of A; b: [K, N].  Returns the full [M, N] C."""
@@ -245,8 +274,10 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chun
 
     Several GPUs: every rank has the same B in host memory, so each uploads only its 1/world of B's
     rows and the ranks all-gather B over NVLink -- world times less PCIe traffic for B than uploading
-    it everywhere.  The slice of B goes first on a copy stream and the A panel behind it, so that A
-    arrives while B is being gathered; then the sharded product, and the C panel comes back.
+    it everywhere.  The slice of B goes first on a copy stream and the A panel behind it in row blocks,
+    so that A arrives while B is being gathered; every block is multiplied when it is there (into
+    all ranks' C in the fused mode) and its rows of C go back to the host while the next block is
+    multiplied.
     """
     dev = a_dev.device
     if sharded.world > 1:
@@ -254,18 +285,40 @@ def mm_from_host(sharded, a_host_panel, b_host, a_dev, b_dev, c_host_panel, chun
         if dev.type == "cuda" and b_dev.shape[0] % sharded.world == 0 and b_dev.is_contiguous():
             lo = sharded.rank * kp
             cur = torch.cuda.current_stream(dev)
-            up, _ = _side_streams(dev)
+            up, down = _side_streams(dev)
+            # row blocks of this rank's panel: multiplied as they arrive, their rows of C sent back while
+            # the next block is multiplied (a rank's own rows of C are written by its own kernel)
+            Mp = a_dev.shape[0]
+            nblocks = 4 if Mp >= 8192 else (2 if Mp >= 2048 else 1)
+            blocks = _row_blocks(Mp, b_dev.shape[1], nblocks,
+                                 torch.cuda.get_device_properties(dev).multi_processor_count) if nblocks > 1 else [(0, Mp)]
             up.wait_stream(cur)  # the buffers may still be in use by what the caller queued before
+            down.wait_stream(cur)
+            a_there = []
             with torch.cuda.stream(up):
                 b_dev[lo:lo + kp].copy_(b_host[lo:lo + kp], non_blocking=True)
                 b_there = torch.cuda.Event()
                 b_there.record(up)
-                a_dev.copy_(a_host_panel, non_blocking=True)
-                a_there = torch.cuda.Event()
-                a_there.record(up)
+                for r0, r1 in blocks:
+                    a_dev[r0:r1].copy_(a_host_panel[r0:r1], non_blocking=True)
+                    ev = torch.cuda.Event()
+                    ev.record(up)
+                    a_there.append(ev)
             cur.wait_event(b_there)
             dist.all_gather_into_tensor(b_dev, b_dev[lo:lo + kp], group=sharded.group)
-            cur.wait_event(a_there)
+            sharded.begin_step()
+            mine = sharded.my_rows()
+            for (r0, r1), ev in zip(blocks, a_there):
+                cur.wait_event(ev)
+                sharded.rows_into_all(a_dev[r0:r1], b_dev, r0)
+                done = torch.cuda.Event()
+                done.record(cur)
+                down.wait_event(done)
+                with torch.cuda.stream(down):
+                    c_host_panel[r0:r1].copy_(mine[r0:r1], non_blocking=True)
+            sharded.end_step()
+            cur.wait_stream(down)
+            return sharded.C
         elif b_dev.shape[0] % sharded.world == 0 and b_dev.is_contiguous():
             lo = sharded.rank * kp
             a_dev.copy_(a_host_panel, non_blocking=True)

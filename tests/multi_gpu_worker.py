@@ -54,6 +54,26 @@ def main():
     torch.cuda.synchronize()
     out["from_host"] = bool(torch.equal(c, alone)) and bool(
         torch.equal(c_host, alone[sh.row0:sh.row0 + sh.Mp].cpu())) and bool(torch.equal(b_dev, b))
+    # a panel tall enough for the step to run in row blocks (each multiplied when it has arrived, its rows
+    # of C sent back while the next one is multiplied), twice on the same buffers
+    Mb, Kb = 4096 * world, 200
+    ab = (torch.rand(Mb, Kb, generator=g) * 2 - 1).to(dev)
+    bb = (torch.rand(Kb, N, generator=g) * 2 - 1).to(dev)
+    alone_b = ops.mm(ab, bb)
+    shb = ShardedMM(Mb, N, Kb, device=dev, mode="auto")
+    ab_host = ab[shb.row0:shb.row0 + shb.Mp].cpu().pin_memory()
+    bb_host = bb.cpu().pin_memory()
+    ab_dev, bb_dev = torch.zeros_like(ab_host, device=dev), torch.zeros_like(bb_host, device=dev)
+    cb_host = torch.zeros(shb.Mp, N).pin_memory()
+    ok = True
+    for rep in range(2):
+        cb_host.zero_()
+        shb.kernel_launches = 0
+        cb = mm_from_host(shb, ab_host, bb_host, ab_dev, bb_dev, cb_host)
+        torch.cuda.synchronize()
+        ok = ok and shb.kernel_launches >= 2 and bool(torch.equal(cb, alone_b)) and bool(
+            torch.equal(cb_host, alone_b[shb.row0:shb.row0 + shb.Mp].cpu()))
+    out["from_host_blocks"] = ok
     gathered = [None] * world
     dist.all_gather_object(gathered, out)
     if rank == 0:

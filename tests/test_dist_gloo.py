@@ -54,6 +54,14 @@ def _worker(rank, world, port, q):
             ok = ok and torch.equal(c_host.view(torch.int32),
                                     full2[sh2.row0:sh2.row0 + sh2.Mp].view(torch.int32))
             ok = ok and torch.equal(b_dev.view(torch.int32), b2.view(torch.int32))
+        # the product block by block (what the pipelined host-operand step issues): same full C
+        sh3 = ShardedMM(M, N, K, device="cpu", mode="nccl", mm_into=mm_into)
+        mine = a[sh3.row0:sh3.row0 + sh3.Mp]
+        sh3.begin_step()
+        for r0, r1 in ((0, 7), (7, 40), (40, sh3.Mp)):
+            sh3.rows_into_all(mine[r0:r1], b, r0)
+        sh3.end_step()
+        ok = ok and sh3.kernel_launches == 3 and torch.equal(sh3.C.view(torch.int32), full.view(torch.int32))
         # convolution sharded by batch: every rank ends with all images, bit-identical
         from repdl_b200.dist import ShardedConv2d
         x = torch.randn(6, 3, 9, 8, generator=g)

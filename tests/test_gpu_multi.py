@@ -28,7 +28,7 @@ def test_row_sharded_mm_matches_single_gpu():
     ranks = json.loads(line[len("RESULT "):])
     assert len(ranks) == world
     for r in ranks:
-        for key in ("nccl_0", "nccl_1", "auto_0", "auto_1", "from_host"):
+        for key in ("nccl_0", "nccl_1", "auto_0", "auto_1", "from_host", "from_host_blocks"):
             assert r[key], (r, key)
         # the GPUs of one B200 node reach each other's memory: "auto" must really have taken the
         # epilogue-store path, not quietly fallen back to NCCL
