@@ -836,6 +836,87 @@ int launch_conv_window(const float *src, const float *kw, float *out, const Conv
     return launch_status();
 }
 
+// ------------------------------------------------------------------------------------------------
+// conv2d with short chains (IC/groups * KH * KW <= 64 taps: a first layer over one or three input
+// planes).  Such a convolution is bound by its output stream, not by FMAs, and the implicit GEMM's
+// gather costs more than the arithmetic.  Here a thread owns one output pixel and CS_OC output
+// channels: it walks the taps in the reference's order (ic, kh, kw), loads its input value of a tap
+// once (coalesced over the pixels of a warp), reads the CS_OC weights of that tap from shared memory
+// by broadcast, and skips a tap that falls into the padding exactly as the reference does (so no
+// operand watch and no fallback are needed).  Stores are coalesced per channel.
+// ------------------------------------------------------------------------------------------------
+constexpr int CS_OC = 32, CS_THREADS = 256, CS_KMAX = 64;
+
+// KB > 0: at most KB taps, all loaded before the first FMA (their latencies overlap); KB = 0: any number up
+// to CS_KMAX, loaded one by one.
+template <int KB>
+__global__ void __launch_bounds__(CS_THREADS)
+conv_short_kernel(const float *__restrict__ X, const float *__restrict__ Wt, float *__restrict__ Y, ConvDims d,
+                  long long npix)
+{
+    __shared__ __align__(16) float Ws[CS_KMAX][CS_OC];
+    __shared__ int toff[CS_KMAX], tkh[CS_KMAX], tkw[CS_KMAX];
+    const int ICg = d.IC / d.groups, OCg = d.OC / d.groups;
+    const int K = ICg * d.KH * d.KW;
+    const int grp = blockIdx.z, oc0 = blockIdx.y * CS_OC;  // oc0 within the group
+    for (int i = threadIdx.x; i < K * CS_OC; i += CS_THREADS) {
+        const int k = i / CS_OC, o = i - k * CS_OC;
+        Ws[k][o] = oc0 + o < OCg ? __ldg(Wt + ((int64_t)(grp * OCg + oc0 + o)) * K + k) : 0.0f;
+    }
+    for (int k = threadIdx.x; k < K; k += CS_THREADS) {
+        const int ic = k / (d.KH * d.KW), r = k - ic * d.KH * d.KW;
+        tkh[k] = r / d.KW, tkw[k] = r - (r / d.KW) * d.KW;
+        toff[k] = (ic * d.H + tkh[k]) * d.W + tkw[k];
+    }
+    __syncthreads();
+    const long long pix = (long long)blockIdx.x * CS_THREADS + threadIdx.x;
+    if (pix >= npix) return;
+    const int OHW = d.OH * d.OW;
+    const int n = (int)(pix / OHW), rem = (int)(pix - (long long)n * OHW);
+    const int oh = rem / d.OW, ow = rem - oh * d.OW;
+    const int h0 = oh * d.sH - d.pH, w0 = ow * d.sW - d.pW;
+    const float *xn = X + ((int64_t)n * d.IC + (int64_t)grp * ICg) * d.H * d.W;
+    const int base = h0 * d.W + w0;  // may be negative; only valid taps are dereferenced
+    float acc[CS_OC];
+#pragma unroll
+    for (int o = 0; o < CS_OC; o++) acc[o] = 0.0f;
+    auto tap = [&](float x, int k) {
+        const float4 *w4 = reinterpret_cast<const float4 *>(Ws[k]);
+#pragma unroll
+        for (int q = 0; q < CS_OC / 4; q++) {
+            const float4 w = w4[q];
+            acc[4 * q + 0] = __fmaf_rn(x, w.x, acc[4 * q + 0]);
+            acc[4 * q + 1] = __fmaf_rn(x, w.y, acc[4 * q + 1]);
+            acc[4 * q + 2] = __fmaf_rn(x, w.z, acc[4 * q + 2]);
+            acc[4 * q + 3] = __fmaf_rn(x, w.w, acc[4 * q + 3]);
+        }
+    };
+    auto in_image = [&](int k) {
+        return (unsigned)(h0 + tkh[k]) < (unsigned)d.H && (unsigned)(w0 + tkw[k]) < (unsigned)d.W;
+    };
+    // the reference skips taps in the padding: nothing is added for them
+    if (KB > 0) {
+        float x[KB > 0 ? KB : 1];
+        unsigned valid = 0;
+#pragma unroll
+        for (int k = 0; k < KB; k++) {
+            const bool v = k < K && in_image(k);
+            x[k] = v ? __ldg(xn + base + toff[k]) : 0.0f;
+            valid |= (v ? 1u : 0u) << k;
+        }
+#pragma unroll
+        for (int k = 0; k < KB; k++)
+            if ((valid >> k) & 1u) tap(x[k], k);
+    } else {
+        for (int k = 0; k < K; k++)
+            if (in_image(k)) tap(__ldg(xn + base + toff[k]), k);
+    }
+    float *yp = Y + ((int64_t)n * d.OC + (int64_t)grp * OCg + oc0) * OHW + rem;
+#pragma unroll
+    for (int o = 0; o < CS_OC; o++)
+        if (oc0 + o < OCg) yp[(int64_t)o * OHW] = acc[o];
+}
+
 template <int MODE>
 int launch_conv_gemm(const float *src, const float *kw, float *out, const ConvDims &d, cudaStream_t st)
 {
@@ -850,7 +931,19 @@ int launch_conv_gemm(const float *src, const float *kw, float *out, const ConvDi
         const int e = launch_conv_window<MODE>(src, kw, out, d, st);
         if (e >= 0) return e;
     }
-    (void)ICg;
+    if (MODE == 0 && ICg * d.KH * d.KW <= CS_KMAX && (int64_t)d.IC * d.H * d.W < 0x7FFFFFFF &&
+        (OCg + CS_OC - 1) / CS_OC <= 65535 && (ncols + CS_THREADS - 1) / CS_THREADS <= 0x7FFFFFFF) {
+        dim3 grid((unsigned)((ncols + CS_THREADS - 1) / CS_THREADS), (unsigned)((OCg + CS_OC - 1) / CS_OC),
+                  (unsigned)groups);
+        const int K = ICg * d.KH * d.KW;
+        if (K <= 16)
+            conv_short_kernel<16><<<grid, CS_THREADS, 0, st>>>(src, kw, out, d, (long long)ncols);
+        else if (K <= 32)
+            conv_short_kernel<32><<<grid, CS_THREADS, 0, st>>>(src, kw, out, d, (long long)ncols);
+        else
+            conv_short_kernel<0><<<grid, CS_THREADS, 0, st>>>(src, kw, out, d, (long long)ncols);
+        return launch_status();
+    }
     const bool s1 = d.sH == 1 && d.sW == 1;
     if (M <= 32) {
         dim3 grid((unsigned)gx, (unsigned)((M + 31) / 32), (unsigned)groups);
