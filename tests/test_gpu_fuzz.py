@@ -123,6 +123,33 @@ def test_conv_window_kernel_random_shapes(cfg):
         assert same(ops.conv2d(xd, k2.cuda(), s, p, 2), oracle.conv2d(x, k2, s, p, 2))
 
 
+SHORT_CHAIN_CONVS = [
+    # N, IC, H, W, OC, KH, KW, stride, padding, groups: at most 64 taps per output
+    (3, 1, 28, 28, 32, 3, 3, (1, 1), (0, 0), 1),   # 9 taps
+    (2, 3, 19, 23, 40, 3, 3, (1, 1), (1, 1), 1),   # 27 taps, channels beyond one block of 32, padding
+    (2, 3, 17, 16, 7, 4, 4, (2, 1), (2, 3), 1),    # 48 taps (the loop form), stride, wide padding
+    (1, 2, 9, 31, 33, 5, 5, (1, 2), (2, 2), 1),    # 50 taps
+    (2, 4, 12, 12, 10, 3, 3, (1, 1), (1, 0), 2),   # groups: 18 taps per output
+    (1, 1, 3, 3, 1, 3, 3, (1, 1), (2, 2), 1),      # more padding than image
+    (2, 7, 10, 11, 5, 3, 3, (3, 2), (1, 1), 1),    # 63 taps
+    (2, 6, 8, 8, 12, 1, 1, (1, 1), (0, 0), 3),     # 1 x 1, grouped: 2 taps
+]
+
+
+@pytest.mark.parametrize("cfg", SHORT_CHAIN_CONVS, ids=lambda c: "x".join(map(str, c[:7])) + "_g%d" % c[9])
+def test_conv_short_chains(cfg):
+    """Forward convolutions with few taps per output (first layers) take the kernel that owns a pixel x 32
+    channels per thread and skips padding taps like the reference; -0 results and tiny operands included."""
+    from repdl_b200 import ops
+    N, IC, H, W, OC, KH, KW, s, p, groups = cfg
+    g = torch.Generator().manual_seed(sum(cfg[:7]) * 31 + groups)
+    x, k = _randn(g, N, IC, H, W), _randn(g, OC, IC // groups, KH, KW)
+    x.view(-1)[::7] = -0.0
+    x.view(-1)[3::11] *= 1e-30
+    k.view(-1)[2::5] *= -1e-25
+    assert bits_equal(ops.conv2d(x.cuda(), k.cuda(), s, p, groups), oracle.conv2d(x, k, s, p, groups))
+
+
 def test_conv_padding_keeps_a_negative_zero():
     """An accumulator can become -0 without any operand being tiny enough for its products to vanish:
     -3 * 2^-149 plus (3 - 2^-22) * 2^-149 rounds to -0.  The padding tap behind it must then leave
