@@ -123,6 +123,31 @@ def test_conv_window_kernel_random_shapes(cfg):
         assert same(ops.conv2d(xd, k2.cuda(), s, p, 2), oracle.conv2d(x, k2, s, p, 2))
 
 
+@pytest.mark.parametrize("cfg", [
+    # N, IC, H, W, OC, KH, KW, stride, padding: weight-gradient chains whose chunks are segments of one
+    # output row (rows longer than a chunk), with and without 16-byte copies of grad_output, padded,
+    # and a whole image per chunk with a ragged last ring
+    (1, 16, 5, 402, 72, 3, 3, (1, 1), (0, 0)),
+    (1, 16, 5, 403, 72, 3, 3, (1, 1), (0, 0)),
+    (2, 16, 4, 900, 72, 3, 3, (1, 1), (1, 1)),
+    (3, 2, 4, 1000, 5, 2, 3, (1, 1), (0, 1)),
+    (5, 3, 27, 31, 9, 3, 3, (1, 1), (0, 0)),
+    (4, 16, 13, 19, 72, 3, 3, (1, 1), (2, 2)),
+], ids=lambda c: "x".join(map(str, c[:7])) + "_p%d%d" % c[8])
+def test_conv_weight_gradient_chunk_geometries(cfg):
+    from repdl_b200 import ops
+    N, IC, H, W, OC, KH, KW, s, p = cfg
+    g = torch.Generator().manual_seed(sum(cfg[:7]))
+    OH, OW = (H + 2 * p[0] - KH) // s[0] + 1, (W + 2 * p[1] - KW) // s[1] + 1
+    x, go = _randn(g, N, IC, H, W), _randn(g, N, OC, OH, OW)
+    want_w = oracle.conv2d_grad_kernel(x, (OC, IC, KH, KW), go, s, p)
+    assert bits_equal(ops.conv2d_grad_kernel(x.cuda(), (OC, IC, KH, KW), go.cuda(), s, p), want_w)
+    fused = ops.conv2d_grad_kernel_bias(x.cuda(), (OC, IC, KH, KW), go.cuda(), s, p)
+    if fused is not None:
+        assert bits_equal(fused[0], want_w)
+        assert bits_equal(fused[1], oracle.sum4d_dim023(go, False, False))
+
+
 SHORT_CHAIN_CONVS = [
     # N, IC, H, W, OC, KH, KW, stride, padding, groups: at most 64 taps per output
     (3, 1, 28, 28, 32, 3, 3, (1, 1), (0, 0), 1),   # 9 taps
