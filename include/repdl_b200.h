@@ -70,6 +70,16 @@ int repdl_b200_mm_allgather(const float *A_rows, const float *B, float *const *C
                             int64_t row0, int64_t M_local, int64_t N, int64_t K, int transA,
                             int transB, int64_t lda, int64_t ldb, int64_t ldc, void *stream);
 
+/* conv2d with the layer's epilogue in the same launch: output = conv2d(input, kernel) + bias[oc], then
+ * max(., 0) if relu != 0.  Replaces the launches of Conv2dFunction.forward behind the operator
+ * (repdl/nn/conv.py:27-28: `output += bias...`) and of a ReLU that follows the layer; each step is the
+ * separately rounded fp32 operation those launches perform (NaN passes through the maximum), so the
+ * bits are the same.  bias may be NULL. */
+int repdl_b200_conv2d_bias_act(const float *input, const float *kernel, const float *bias, float *output,
+                               int64_t N, int64_t IC, int64_t H, int64_t W, int64_t OC, int64_t KH,
+                               int64_t KW, int64_t sH, int64_t sW, int64_t pH, int64_t pW,
+                               int64_t groups, int relu, void *stream);
+
 /* ---- convolution -----------------------------------------------------------------------
  * Replace repdl::cuda::convolution::{conv2d, conv2d_grad_input, conv2d_grad_kernel}
  * (backend/cuda/convolution.cu:153-173, 259-277, 359-377); bits defined by

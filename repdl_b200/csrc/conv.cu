@@ -30,7 +30,20 @@ namespace {
 struct ConvDims {
     int N, IC, H, W, OC, KH, KW, OH, OW, sH, sW, pH, pW, groups;
     unsigned long long m40_khw, m40_kw, m40_ow;  // ceil(2^40 / (KH*KW)), / KW, / OW: division by multiplication
+    // epilogue of the forward convolution (repdl_b200_conv2d_bias_act): bias[oc] is added to the finished
+    // chain with one separately rounded fp32 addition, then max(., 0); both are what the layer's own
+    // element-wise kernels would do to the stored result, so the bits are the same
+    const float *bias;
+    int relu;
 };
+
+// the two epilogue steps on one finished output of channel oc (NaN passes through the maximum, as in ATen's clamp)
+__device__ __forceinline__ float conv_finish(float v, const ConvDims &d, int oc)
+{
+    if (d.bias) v = __fadd_rn(v, __ldg(d.bias + oc));
+    if (d.relu) v = v != v ? v : fmaxf(v, 0.0f);
+    return v;
+}
 
 // k / dv with m40 = ceil(2^40 / dv): exact whenever k * dv < 2^40 (callers keep k < 2^24, dv < 2^16).
 __device__ __forceinline__ int fastdiv(int k, unsigned long long m40)
@@ -71,7 +84,7 @@ conv2d_direct_kernel(const float *__restrict__ I, const float *__restrict__ Kw,
             }
         }
     }
-    O[idx] = acc;
+    O[idx] = conv_finish(acc, d, oc);
 }
 
 // conv2d_grad_input: backend/cpu/convolution.cpp:65-88.  Thread -> (n, ic, h, w), w fastest.
@@ -418,6 +431,10 @@ conv_gemm_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, fl
                                      : conv2d_grad_input_exact(Src, Kw, d, nn, plane, pp / outW, pp % outW);
                 }
             }
+            if (MODE == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) c[j] = conv_finish(c[j], d, plane);
+            }
             float *dst = Out + ((int64_t)n * planes + plane) * outHW + p;
             if (p + 3 < outHW && (outHW & 3) == 0 && (reinterpret_cast<uintptr_t>(Out) & 15u) == 0) {
                 *reinterpret_cast<float4 *>(dst) = make_float4(c[0], c[1], c[2], c[3]);
@@ -753,6 +770,10 @@ conv_window_kernel(const float *__restrict__ Src, const float *__restrict__ Kw, 
                                          : conv2d_grad_input_exact(Src, Kw, d, n, plane, row, gcol[h] + j);
                 }
             }
+            if (MODE == 0) {
+#pragma unroll
+                for (int j = 0; j < 4; j++) c[j] = conv_finish(c[j], d, plane);
+            }
             float *dst = Out + (((int64_t)n * planes_out + plane) * w.outH + row) * w.outW + gcol[h];
             if (gcol[h] + 3 < w.outW && (reinterpret_cast<uintptr_t>(dst) & 15u) == 0) {
                 *reinterpret_cast<float4 *>(dst) = make_float4(c[0], c[1], c[2], c[3]);
@@ -914,7 +935,7 @@ conv_short_kernel(const float *__restrict__ X, const float *__restrict__ Wt, flo
     float *yp = Y + ((int64_t)n * d.OC + (int64_t)grp * OCg + oc0) * OHW + rem;
 #pragma unroll
     for (int o = 0; o < CS_OC; o++)
-        if (oc0 + o < OCg) yp[(int64_t)o * OHW] = acc[o];
+        if (oc0 + o < OCg) yp[(int64_t)o * OHW] = conv_finish(acc[o], d, grp * OCg + oc0 + o);
 }
 
 template <int MODE>
@@ -1537,6 +1558,7 @@ int fill_dims(ConvDims &d, int64_t N, int64_t IC, int64_t H, int64_t W, int64_t 
     d.N = (int)N; d.IC = (int)IC; d.H = (int)H; d.W = (int)W; d.OC = (int)OC;
     d.KH = (int)KH; d.KW = (int)KW; d.sH = (int)sH; d.sW = (int)sW; d.pH = (int)pH; d.pW = (int)pW;
     d.groups = (int)groups;
+    d.bias = nullptr, d.relu = 0;
     d.OH = (int)((H + 2 * pH - KH) / sH + 1);
     d.OW = (int)((W + 2 * pW - KW) / sW + 1);
     const unsigned long long khw = (unsigned long long)(KH * KW), kwv = (unsigned long long)KW;
@@ -1564,10 +1586,20 @@ extern "C" int repdl_b200_conv2d(const float *input, const float *kernel, float 
                                  int64_t KW, int64_t sH, int64_t sW, int64_t pH, int64_t pW,
                                  int64_t groups, void *stream)
 {
+    return repdl_b200_conv2d_bias_act(input, kernel, nullptr, output, N, IC, H, W, OC, KH, KW, sH, sW, pH, pW,
+                                      groups, 0, stream);
+}
+
+extern "C" int repdl_b200_conv2d_bias_act(const float *input, const float *kernel, const float *bias,
+                                          float *output, int64_t N, int64_t IC, int64_t H, int64_t W, int64_t OC,
+                                          int64_t KH, int64_t KW, int64_t sH, int64_t sW, int64_t pH, int64_t pW,
+                                          int64_t groups, int relu, void *stream)
+{
     clear_stale_error();
     ConvDims d;
     int e = fill_dims(d, N, IC, H, W, OC, KH, KW, sH, sW, pH, pW, groups);
     if (e) return e;
+    d.bias = bias, d.relu = relu ? 1 : 0;
     int64_t total = (int64_t)d.N * d.OC * d.OH * d.OW;
     if (total == 0) return REPDL_OK;
     if (!input || !kernel || !output) return REPDL_E_NULL;

@@ -143,13 +143,17 @@ class Linear(torch.nn.Linear):
 
 class _Conv2d(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, weight, bias, stride, padding, groups):
-        ctx.save_for_backward(x, weight)
+    def forward(ctx, x, weight, bias, stride, padding, groups, relu=False):
         ctx.bias_ref = bias
         ctx.cfg = (stride, padding, groups)
-        out = ops.conv2d(x, weight, stride, padding, groups)
-        if bias is not None:
-            out += bias.unsqueeze(-1).unsqueeze(-1)
+        ctx.relu = bool(relu)
+        # the bias addition (repdl/nn/conv.py:27-28) and, if asked for, the ReLU behind the layer run in the
+        # convolution's epilogue: the same separately rounded operations, two launches fewer each
+        out = ops.conv2d(x, weight, stride, padding, groups, bias=bias, relu=relu)
+        if relu:
+            ctx.save_for_backward(x, weight, out)
+        else:
+            ctx.save_for_backward(x, weight)
         return out
 
     @staticmethod
@@ -157,7 +161,11 @@ class _Conv2d(torch.autograd.Function):
         stride, padding, groups = ctx.cfg
         if groups != 1:
             raise NotImplementedError("grouped convolution has no backward (as in the reference)")
-        x, weight = ctx.saved_tensors
+        if ctx.relu:
+            x, weight, out = ctx.saved_tensors
+            g = torch.ops.aten.threshold_backward(g, out, 0)  # what autograd runs for a ReLU module
+        else:
+            x, weight = ctx.saved_tensors
         need = ctx.needs_input_grad
         if need[1] and need[2]:
             # the weight / bias gradient chains go to a side stream that is only joined at the end
@@ -166,7 +174,7 @@ class _Conv2d(torch.autograd.Function):
                              (g, x), (weight, ctx.bias_ref))
             if late is not None:
                 gx = ops.conv2d_grad_input(x.shape, weight, g, stride, padding) if need[0] else None
-                return gx, late[0], late[1], None, None, None
+                return gx, late[0], late[1], None, None, None, None
         if need[1] and need[2]:
             # weight and bias gradient from one pass over g (the bias chain rides on the row operand of
             # the weight-gradient kernel); the input gradient overlaps on a side stream
@@ -179,11 +187,11 @@ class _Conv2d(torch.autograd.Function):
                 fused,
                 (lambda: ops.conv2d_grad_input(x.shape, weight, g, stride, padding)) if need[0] else None)
             if box["r"] is not None:
-                return gx, box["r"][0], box["r"][1], None, None, None
+                return gx, box["r"][0], box["r"][1], None, None, None, None
             gb, gw = _concurrently(
                 lambda: ops.sum4d_dim023(g),
                 lambda: ops.conv2d_grad_kernel(x, weight.shape, g, stride, padding))
-            return gx, gw, gb, None, None, None
+            return gx, gw, gb, None, None, None, None
         # launch order matters: the two latency-bound operators first (measured on B200 for the second
         # layer of the CNN workload: 0.95 ms in this order, 1.22 ms with the weight gradient first, 1.34 ms
         # with the throughput-bound input gradient first, 1.38 ms one after the other)
@@ -191,24 +199,27 @@ class _Conv2d(torch.autograd.Function):
             (lambda: ops.sum4d_dim023(g)) if need[2] else None,
             (lambda: ops.conv2d_grad_kernel(x, weight.shape, g, stride, padding)) if need[1] else None,
             (lambda: ops.conv2d_grad_input(x.shape, weight, g, stride, padding)) if need[0] else None)
-        return gx, gw, gb, None, None, None
+        return gx, gw, gb, None, None, None, None
 
 
 def _pair(v):
     return (v, v) if isinstance(v, int) else tuple(v)
 
 
-def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1):
+def conv2d(x, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, relu=False):
     if isinstance(padding, str) or _pair(dilation) != (1, 1) or x.dim() != 4:
         raise NotImplementedError("conv2d: string padding, dilation and non-4-d inputs are unsupported")
-    return _Conv2d.apply(x, weight, bias, _pair(stride), _pair(padding), groups)
+    return _Conv2d.apply(x, weight, bias, _pair(stride), _pair(padding), groups, relu)
 
 
 class Conv2d(torch.nn.Conv2d):
+    fused_relu = False  # set by from_torch_module(..., fuse_relu=True) when a ReLU module follows the layer
+
     def forward(self, x):
         if self.padding_mode != "zeros":
             raise NotImplementedError("padding_mode must be 'zeros'")
-        return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups)
+        return conv2d(x, self.weight, self.bias, self.stride, self.padding, self.dilation, self.groups,
+                      self.fused_relu)
 
 
 class _CrossEntropy(torch.autograd.Function):
@@ -246,10 +257,15 @@ class CrossEntropyLoss(torch.nn.CrossEntropyLoss):
 _SWAPS = {torch.nn.Linear: Linear, torch.nn.Conv2d: Conv2d, torch.nn.CrossEntropyLoss: CrossEntropyLoss}
 
 
-def from_torch_module(module):
+def from_torch_module(module, fuse_relu=False):
     """Returns a copy of `module` in which every torch.nn.Linear / Conv2d / CrossEntropyLoss (exact
     types only) is replaced by its reproducible twin sharing the same parameter values; Sequential
-    containers are rebuilt and any other module is shallow-copied with converted children."""
+    containers are rebuilt and any other module is shallow-copied with converted children.
+
+    fuse_relu: inside a Sequential, a torch.nn.ReLU (exact type, not in-place-sensitive: its input is
+    not used elsewhere) that directly follows a Conv2d is folded into the convolution's epilogue and
+    replaced by torch.nn.Identity (the indices of the other modules, and so the state_dict keys, do not
+    change).  Same bits; one forward launch less per pair."""
     cls = _SWAPS.get(type(module))
     if cls is Linear:
         new = Linear(module.in_features, module.out_features, module.bias is not None,
@@ -266,9 +282,15 @@ def from_torch_module(module):
         return CrossEntropyLoss(weight=module.weight, ignore_index=module.ignore_index,
                                 reduction=module.reduction, label_smoothing=module.label_smoothing)
     if type(module) is torch.nn.Sequential:
-        return torch.nn.Sequential(*[from_torch_module(m) for m in module])
+        mods = [from_torch_module(m, fuse_relu) for m in module]
+        if fuse_relu:
+            for i in range(len(mods) - 1):
+                if type(mods[i]) is Conv2d and type(mods[i + 1]) is torch.nn.ReLU:
+                    mods[i].fused_relu = True
+                    mods[i + 1] = torch.nn.Identity()
+        return torch.nn.Sequential(*mods)
     new = copy(module)
     new._modules = dict(new._modules)
     for name, child in module.named_children():
-        new._modules[name] = from_torch_module(child)
+        new._modules[name] = from_torch_module(child, fuse_relu)
     return new

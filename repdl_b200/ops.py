@@ -59,7 +59,10 @@ def _out_extent(size, pad, k, stride, what):
     return (size + 2 * pad - k) // stride + 1
 
 
-def conv2d(input, weight, stride, padding, groups) -> torch.Tensor:
+def conv2d(input, weight, stride, padding, groups, bias=None, relu=False) -> torch.Tensor:
+    """conv2d of the reference (repdl/ops.py), optionally with the layer's epilogue in the same launch:
+    `+ bias[oc]` (what Conv2dFunction.forward does next, repdl/nn/conv.py:27-28) and `max(., 0)` (a ReLU
+    behind the layer); same bits as the separate element-wise kernels."""
     _need(input, "input", 4), _need(weight, "weight", 4)
     x, k = input.contiguous(), weight.contiguous()
     N, IC, H, W = x.shape
@@ -69,10 +72,16 @@ def conv2d(input, weight, stride, padding, groups) -> torch.Tensor:
     OH = _out_extent(H, padding[0], KH, stride[0], "conv2d")
     OW = _out_extent(W, padding[1], KW, stride[1], "conv2d")
     out = torch.empty((N, OC, OH, OW), dtype=torch.float32, device=x.device)
+    b = None
+    if bias is not None:
+        _need(bias, "bias", 1)
+        if bias.shape[0] != OC or bias.device != x.device:
+            raise ValueError("conv2d: bias must hold one value per output channel, on the input's device")
+        b = bias.contiguous()
     with torch.cuda.device(x.device):
-        check(lib.repdl_b200_conv2d(x.data_ptr(), k.data_ptr(), out.data_ptr(), N, IC, H, W, OC, KH,
-                                    KW, stride[0], stride[1], padding[0], padding[1], groups,
-                                    _stream(x)), "conv2d")
+        check(lib.repdl_b200_conv2d_bias_act(x.data_ptr(), k.data_ptr(), b.data_ptr() if b is not None else None,
+                                             out.data_ptr(), N, IC, H, W, OC, KH, KW, stride[0], stride[1],
+                                             padding[0], padding[1], groups, int(bool(relu)), _stream(x)), "conv2d")
     return out
 
 

@@ -42,13 +42,15 @@ def _train(model, loss_fn, x, y, steps, checkpoints):
 
 
 @pytest.mark.skipif(not os.path.exists(GOLD), reason="cnn_steps.json not generated")
-def test_cnn_training_matches_reference_cpu_hashes():
+@pytest.mark.parametrize("fuse_relu", [False, True], ids=["layers_as_given", "relu_in_the_conv_epilogue"])
+def test_cnn_training_matches_reference_cpu_hashes(fuse_relu):
     from cases import sha
     from repdl_b200 import nn as rnn
     from repdl_b200 import workloads
     gold = json.load(open(GOLD))
     torch.manual_seed(3)
-    model = rnn.from_torch_module(workloads.cnn_torch_model())
+    model = rnn.from_torch_module(workloads.cnn_torch_model(), fuse_relu=fuse_relu)
+    assert sum(type(m) is torch.nn.Identity for m in model) == (2 if fuse_relu else 0)
     x, y = workloads.cnn_batch(256)
     assert [sha(x), sha(y)] == gold["input_sha256"]
     assert _hash_params(model) == gold["init_params"]

@@ -148,6 +148,35 @@ def test_conv_weight_gradient_chunk_geometries(cfg):
         assert bits_equal(fused[1], oracle.sum4d_dim023(go, False, False))
 
 
+@pytest.mark.parametrize("cfg", [
+    # N, IC, H, W, OC, KH, KW, stride, padding, groups: one shape per forward kernel (short chains, the staged
+    # window, the implicit GEMM with 32 and 64 channels per tile, the direct loop)
+    (2, 3, 12, 13, 40, 3, 3, (1, 1), (1, 1), 1),
+    (2, 16, 12, 13, 40, 3, 3, (1, 1), (1, 1), 1),
+    (2, 16, 12, 13, 24, 5, 2, (2, 1), (1, 0), 1),
+    (2, 16, 12, 13, 70, 4, 4, (1, 2), (0, 2), 2),
+    (1, 2, 20, 9, 3, 9, 9, (1, 1), (4, 4), 1),
+], ids=lambda c: "x".join(map(str, c[:7])) + "_g%d" % c[9])
+def test_conv_epilogue_bias_and_relu(cfg):
+    """conv2d with bias and ReLU in the kernel's epilogue equals the three separate launches (and the
+    oracle's convolution followed by the same two element-wise operations), NaN and -0 included."""
+    from repdl_b200 import ops
+    N, IC, H, W, OC, KH, KW, s, p, groups = cfg
+    g = torch.Generator().manual_seed(sum(cfg[:7]) + 5)
+    x, k, b = _randn(g, N, IC, H, W), _randn(g, OC, IC // groups, KH, KW), _randn(g, OC)
+    x.view(-1)[1] = float("nan")
+    b[0] = -0.0
+    k[0] = 0.0          # channel 0: conv = +0 (or NaN), + -0 -> +0; relu keeps +0
+    want = oracle.conv2d(x, k, s, p, groups) + b.view(1, -1, 1, 1)
+    xd, kd, bd = x.cuda(), k.cuda(), b.cuda()
+    plain = ops.conv2d(xd, kd, s, p, groups)
+    assert equal_up_to_nan_payload(ops.conv2d(xd, kd, s, p, groups, bias=bd), plain + bd.view(1, -1, 1, 1))
+    assert equal_up_to_nan_payload(ops.conv2d(xd, kd, s, p, groups, bias=bd), want)
+    fused = ops.conv2d(xd, kd, s, p, groups, bias=bd, relu=True)
+    assert equal_up_to_nan_payload(fused, torch.relu(plain + bd.view(1, -1, 1, 1)))
+    assert equal_up_to_nan_payload(ops.conv2d(xd, kd, s, p, groups, relu=True), torch.relu(plain))
+
+
 SHORT_CHAIN_CONVS = [
     # N, IC, H, W, OC, KH, KW, stride, padding, groups: at most 64 taps per output
     (3, 1, 28, 28, 32, 3, 3, (1, 1), (0, 0), 1),   # 9 taps
