@@ -42,6 +42,17 @@ int repdl_b200_sm_arch(void);
 /* Human-readable text for a status returned by any call below (static storage). */
 const char *repdl_b200_strerror(int status);
 
+/* Max pooling over non-overlapping windows (kernel = stride, no padding, no dilation, floor mode) of
+ * `planes` = N * C planes of H x W, and its backward pass.  Not operators of the reference's backend: its
+ * layers call torch.nn.functional.max_pool2d, which these replace behind repdl_b200.nn.MaxPool2d.  The
+ * forward scan keeps ATen's selection rule (row by row; a value is taken if it is greater than the maximum
+ * so far or is a NaN), so the result and the position that receives the gradient are the ones torch picks.
+ * index: int32, position h * W + w inside the plane.  Output extent: (H / KH) x (W / KW). */
+int repdl_b200_maxpool2d(const float *x, float *y, int *index, int64_t planes, int64_t H, int64_t W,
+                         int64_t KH, int64_t KW, void *stream);
+int repdl_b200_maxpool2d_backward(const float *grad_y, const int *index, float *grad_x, int64_t planes,
+                                  int64_t H, int64_t W, int64_t KH, int64_t KW, void *stream);
+
 /* Strided sub-matrix copy on a stream: `rows` rows of `width_bytes` bytes, source and destination
  * with their own row pitches.  direction 0: host -> device, 1: device -> host, 2: device -> device.
  * No counterpart in the reference (its operators take whole tensors that live on the device): the

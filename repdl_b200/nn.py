@@ -222,6 +222,50 @@ class Conv2d(torch.nn.Conv2d):
                       self.fused_relu)
 
 
+class _MaxPool2d(torch.autograd.Function):
+    """max_pool2d over non-overlapping windows on the library's two streaming kernels (torch's backward
+    kernel is written for overlapping windows).  Same maximum, same position for the gradient."""
+
+    @staticmethod
+    def forward(ctx, x, kh, kw):
+        from ._cabi import check, lib
+        x = x.contiguous()
+        N, C, H, W = x.shape
+        y = torch.empty((N, C, H // kh, W // kw), dtype=torch.float32, device=x.device)
+        idx = torch.empty(y.shape, dtype=torch.int32, device=x.device)
+        with torch.cuda.device(x.device):
+            check(lib.repdl_b200_maxpool2d(x.data_ptr(), y.data_ptr(), idx.data_ptr(), N * C, H, W, kh, kw,
+                                           torch.cuda.current_stream(x.device).cuda_stream), "maxpool2d")
+        ctx.save_for_backward(idx)
+        ctx.geom = (tuple(x.shape), kh, kw)
+        return y
+
+    @staticmethod
+    def backward(ctx, g):
+        from ._cabi import check, lib
+        (idx,) = ctx.saved_tensors
+        shape, kh, kw = ctx.geom
+        g = g.contiguous()
+        gx = torch.empty(shape, dtype=torch.float32, device=g.device)
+        with torch.cuda.device(g.device):
+            check(lib.repdl_b200_maxpool2d_backward(g.data_ptr(), idx.data_ptr(), gx.data_ptr(), shape[0] * shape[1],
+                                                    shape[2], shape[3], kh, kw,
+                                                    torch.cuda.current_stream(g.device).cuda_stream),
+                  "maxpool2d_backward")
+        return gx, None, None
+
+
+class MaxPool2d(torch.nn.MaxPool2d):
+    def forward(self, x):
+        k = _pair(self.kernel_size)
+        s = _pair(self.stride if self.stride is not None else self.kernel_size)
+        if (x.is_cuda and x.dtype == torch.float32 and x.dim() == 4 and k == s and _pair(self.padding) == (0, 0)
+                and _pair(self.dilation) == (1, 1) and not self.ceil_mode and not self.return_indices
+                and x.shape[2] >= k[0] and x.shape[3] >= k[1] and x.numel() > 0):
+            return _MaxPool2d.apply(x, k[0], k[1])
+        return super().forward(x)  # overlapping or padded windows: torch's kernels
+
+
 class _CrossEntropy(torch.autograd.Function):
     @staticmethod
     def forward(ctx, logits, target):
@@ -254,12 +298,14 @@ class CrossEntropyLoss(torch.nn.CrossEntropyLoss):
         return cross_entropy(logits, target)
 
 
-_SWAPS = {torch.nn.Linear: Linear, torch.nn.Conv2d: Conv2d, torch.nn.CrossEntropyLoss: CrossEntropyLoss}
+_SWAPS = {torch.nn.Linear: Linear, torch.nn.Conv2d: Conv2d, torch.nn.CrossEntropyLoss: CrossEntropyLoss,
+          torch.nn.MaxPool2d: MaxPool2d}
 
 
 def from_torch_module(module, fuse_relu=False):
     """Returns a copy of `module` in which every torch.nn.Linear / Conv2d / CrossEntropyLoss (exact
-    types only) is replaced by its reproducible twin sharing the same parameter values; Sequential
+    types only) is replaced by its reproducible twin sharing the same parameter values (and every
+    torch.nn.MaxPool2d by one that runs non-overlapping windows on this library's kernels); Sequential
     containers are rebuilt and any other module is shallow-copied with converted children.
 
     fuse_relu: inside a Sequential, a torch.nn.ReLU (exact type, not in-place-sensitive: its input is
@@ -278,6 +324,9 @@ def from_torch_module(module, fuse_relu=False):
                      module.padding_mode, device=module.weight.device, dtype=module.weight.dtype)
         new.load_state_dict(module.state_dict())
         return new
+    if cls is MaxPool2d:
+        return MaxPool2d(module.kernel_size, module.stride, module.padding, module.dilation,
+                         module.return_indices, module.ceil_mode)
     if cls is CrossEntropyLoss:
         return CrossEntropyLoss(weight=module.weight, ignore_index=module.ignore_index,
                                 reduction=module.reduction, label_smoothing=module.label_smoothing)

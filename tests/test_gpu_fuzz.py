@@ -177,6 +177,35 @@ def test_conv_epilogue_bias_and_relu(cfg):
     assert equal_up_to_nan_payload(ops.conv2d(xd, kd, s, p, groups, relu=True), torch.relu(plain))
 
 
+@pytest.mark.parametrize("cfg", [(3, 5, 24, 24, 2, 2), (2, 3, 13, 17, 2, 2), (1, 4, 9, 10, 3, 3), (2, 2, 7, 31, 2, 3),
+                                 (1, 1, 2, 2, 2, 2), (4, 6, 5, 5, 5, 5)], ids=lambda c: "x".join(map(str, c)))
+def test_maxpool_over_disjoint_windows(cfg):
+    """repdl_b200.nn.MaxPool2d (kernel = stride) against torch's CPU max_pool2d, forward and backward:
+    ties (many equal values, zeros of both signs), NaNs and rows / columns beyond the last whole window."""
+    from repdl_b200 import nn as rnn
+    N, C, H, W, kh, kw = cfg
+    g = torch.Generator().manual_seed(sum(cfg))
+    x = torch.randint(-2, 3, (N, C, H, W), generator=g).float()      # few distinct values: ties everywhere
+    x.view(-1)[::5] *= _randn(g, x.view(-1)[::5].numel())
+    x.view(-1)[3::17] = -0.0
+    if x.numel() > 40:
+        x.view(-1)[7::41] = float("nan")
+    xc = x.clone().requires_grad_(True)
+    yc = torch.nn.functional.max_pool2d(xc, (kh, kw))
+    go = _randn(g, *yc.shape)
+    yc.backward(go)
+    pool = rnn.from_torch_module(torch.nn.Sequential(torch.nn.MaxPool2d((kh, kw))))[0]
+    assert type(pool) is rnn.MaxPool2d
+    xd = x.cuda().requires_grad_(True)
+    yd = pool(xd)
+    yd.backward(go.cuda())
+    assert equal_up_to_nan_payload(yd, yc) and bits_equal(xd.grad, xc.grad)
+    # windows that overlap are left to torch
+    if H >= 3 and W >= 3:
+        over = rnn.MaxPool2d(3, stride=2)
+        assert equal_up_to_nan_payload(over(x.cuda()), torch.nn.functional.max_pool2d(x, 3, 2))
+
+
 SHORT_CHAIN_CONVS = [
     # N, IC, H, W, OC, KH, KW, stride, padding, groups: at most 64 taps per output
     (3, 1, 28, 28, 32, 3, 3, (1, 1), (0, 0), 1),   # 9 taps
