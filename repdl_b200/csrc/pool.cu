@@ -64,6 +64,32 @@ maxpool_backward_kernel(const float *__restrict__ GY, const int *__restrict__ ID
     }
 }
 
+// four consecutive columns per thread (W a multiple of 4, 16-byte aligned gradient): one row decode and one
+// 16-byte store for four elements
+__global__ void __launch_bounds__(POOL_THREADS)
+maxpool_backward4_kernel(const float *__restrict__ GY, const int *__restrict__ IDX, float *__restrict__ GX,
+                         unsigned total4, int H, int W, int OH, int OW, int KH, int KW)
+{
+    const unsigned stride = gridDim.x * POOL_THREADS, W4 = (unsigned)W / 4;
+    for (unsigned i = blockIdx.x * POOL_THREADS + threadIdx.x; i < total4; i += stride) {
+        const unsigned r = i / W4;
+        const int w0 = (int)(i - r * W4) * 4;
+        const unsigned plane = r / (unsigned)H;
+        const int h = (int)(r - plane * (unsigned)H);
+        const int oh = h / KH;
+        float g[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        if (oh < OH) {
+            const int64_t orow = ((int64_t)plane * OH + oh) * OW;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const int ow = (w0 + j) / KW;
+                if (ow < OW && __ldg(IDX + orow + ow) == h * W + w0 + j) g[j] = __ldg(GY + orow + ow);
+            }
+        }
+        *reinterpret_cast<float4 *>(GX + (int64_t)i * 4) = make_float4(g[0], g[1], g[2], g[3]);
+    }
+}
+
 static unsigned pool_grid(int64_t total)
 {
     int64_t blocks = (total + POOL_THREADS - 1) / POOL_THREADS;
@@ -103,7 +129,10 @@ extern "C" int repdl_b200_maxpool2d_backward(const float *grad_y, const int *ind
     const int64_t OH = H / KH, OW = W / KW, total = planes * H * W;
     if (total == 0) return REPDL_OK;
     if (!grad_y || !index || !grad_x) return REPDL_E_NULL;
-    if (total < 0x7FFFFFFF)
+    if (total < 0x7FFFFFFF && W % 4 == 0 && aligned16(grad_x))
+        maxpool_backward4_kernel<<<pool_grid(total / 4), POOL_THREADS, 0, (cudaStream_t)stream>>>(
+            grad_y, index, grad_x, (unsigned)(total / 4), (int)H, (int)W, (int)OH, (int)OW, (int)KH, (int)KW);
+    else if (total < 0x7FFFFFFF)
         maxpool_backward_kernel<unsigned><<<pool_grid(total), POOL_THREADS, 0, (cudaStream_t)stream>>>(
             grad_y, index, grad_x, total, (int)H, (int)W, (int)OH, (int)OW, (int)KH, (int)KW);
     else
