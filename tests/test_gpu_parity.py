@@ -235,6 +235,28 @@ def test_mm_from_host_wave_aligned_blocks_and_column_parts(ops):
         assert torch.equal(c_host.view(torch.int32), want.cpu().view(torch.int32))
 
 
+def test_strided_copy_entry_point(ops):
+    """repdl_b200_copy2d: a column block of a pinned host matrix to the device, device to device, and back;
+    bad arguments are refused before anything is queued."""
+    from repdl_b200._cabi import lib
+    g = torch.Generator().manual_seed(5)
+    h = torch.rand(37, 50, generator=g).pin_memory()
+    d = torch.zeros(37, 64, device="cuda")
+    d2 = torch.zeros(40, 20, device="cuda")
+    back = torch.zeros(37, 20).pin_memory()
+    st = torch.cuda.current_stream().cuda_stream
+    assert lib.repdl_b200_copy2d(d.data_ptr() + 4 * 8, 4 * 64, h.data_ptr() + 4 * 30, 4 * 50, 4 * 20, 37, 0, st) == 0
+    assert lib.repdl_b200_copy2d(d2.data_ptr(), 4 * 20, d.data_ptr() + 4 * 8, 4 * 64, 4 * 20, 37, 2, st) == 0
+    assert lib.repdl_b200_copy2d(back.data_ptr(), 4 * 20, d2.data_ptr(), 4 * 20, 4 * 20, 37, 1, st) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(back, h[:, 30:50]) and torch.equal(d[:, 8:28].cpu(), h[:, 30:50])
+    assert float(d[:, :8].abs().sum()) == 0.0 and float(d[:, 28:].abs().sum()) == 0.0 and float(d2[37:].abs().sum()) == 0.0
+    assert lib.repdl_b200_copy2d(d.data_ptr(), 4 * 10, h.data_ptr(), 4 * 50, 4 * 20, 37, 0, st) < 0   # pitch < width
+    assert lib.repdl_b200_copy2d(d.data_ptr(), 4 * 64, h.data_ptr(), 4 * 50, 4 * 20, 37, 7, st) < 0   # direction
+    assert lib.repdl_b200_copy2d(None, 4 * 64, h.data_ptr(), 4 * 50, 4 * 20, 37, 0, st) < 0
+    assert lib.repdl_b200_copy2d(None, 4 * 64, None, 4 * 50, 0, 37, 0, st) == 0                       # nothing to copy
+
+
 def test_config3_full_chain_and_rows(ops):
     """Config 3 at full size: the 2^30-element chain (checked against the reference's running
     state after every quarter and at the end) and the [65536, 4096] row sums."""
