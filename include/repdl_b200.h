@@ -195,6 +195,13 @@ int repdl_b200_softmax(const float *x, float *y, int64_t M, int64_t N, void *str
 int repdl_b200_cross_entropy(const float *x, const int64_t *target, float *loss, int64_t M,
                              int64_t N, float *row_scratch, void *stream);
 
+/* Gradient of repdl_b200_cross_entropy with respect to x in one launch: replaces the softmax, one_hot,
+ * subtraction and two scalings of CrossEntropyFunction.backward (repdl/nn/loss.py:29-33) with the same
+ * separately rounded operations: (softmax(x) - one_hot(target)) * float(1.0 / M) * grad_loss[0].
+ * grad_loss: one float on the device (the incoming gradient of the mean loss). */
+int repdl_b200_cross_entropy_grad(const float *x, const int64_t *target, const float *grad_loss,
+                                  float *grad_x, int64_t M, int64_t N, void *stream);
+
 /* ---- optimizer steps ---------------------------------------------------------------------------
  * One launch updates up to 24 parameter tensors (more: several launches).  params / grads / ... are
  * HOST arrays of `ntensors` device pointers, sizes holds the element counts.  Every operation is

@@ -26,6 +26,7 @@ SIGNATURES = {
     "repdl_b200_conv2d_bias_act": (_int, [_ptr, _ptr, _ptr, _ptr] + [_i64] * 12 + [_int, _ptr]),
     "repdl_b200_maxpool2d": (_int, [_ptr, _ptr, _ptr] + [_i64] * 5 + [_ptr]),
     "repdl_b200_maxpool2d_backward": (_int, [_ptr, _ptr, _ptr] + [_i64] * 5 + [_ptr]),
+    "repdl_b200_cross_entropy_grad": (_int, [_ptr, _ptr, _ptr, _ptr, _i64, _i64, _ptr]),
     "repdl_b200_copy2d": (_int, [_ptr, _i64, _ptr, _i64, _i64, _i64, _int, _ptr]),
     "repdl_b200_conv2d_grad_input": (_int, [_ptr, _ptr, _ptr] + [_i64] * 11 + [_ptr]),
     "repdl_b200_conv2d_grad_kernel": (_int, [_ptr, _ptr, _ptr] + [_i64] * 11 + [_ptr]),

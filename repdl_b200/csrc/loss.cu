@@ -64,10 +64,50 @@ xent_rows_kernel(const float *__restrict__ x, const int64_t *__restrict__ target
     per_row[i] = __fsub_rn(cr_log(s), zt);
 }
 
+// Gradient of the mean cross-entropy loss with respect to the logits, one row per thread: the softmax
+// of softmax_rows_kernel, then the three separately rounded steps of the reference's backward
+// (repdl/nn/loss.py:29-33): minus one_hot(target), times float(1 / M), times the incoming gradient.
+__global__ void __launch_bounds__(LOSS_THREADS)
+xent_grad_rows_kernel(const float *__restrict__ x, const int64_t *__restrict__ target, const float *__restrict__ g,
+                      float *__restrict__ y, int64_t M, int64_t N, float inv_m)
+{
+    int64_t i = (int64_t)blockIdx.x * LOSS_THREADS + threadIdx.x;
+    if (i >= M) return;
+    const float *row = x + i * N;
+    float *out = y + i * N;
+    const float m = row_max(row, N);
+    float s = 0.0f;
+    for (int64_t j = 0; j < N; j++) {
+        float e = cr_exp(__fsub_rn(__ldg(row + j), m));
+        out[j] = e;
+        s = __fadd_rn(s, e);
+    }
+    const int64_t t = target[i];
+    const float gin = __ldg(g);
+    for (int64_t j = 0; j < N; j++) {
+        float v = __fsub_rn(cr_div(out[j], s), j == t ? 1.0f : 0.0f);
+        v = __fmul_rn(v, inv_m);
+        out[j] = __fmul_rn(v, gin);
+    }
+}
+
 }  // namespace
 }  // namespace repdl_b200
 
 using namespace repdl_b200;
+
+extern "C" int repdl_b200_cross_entropy_grad(const float *x, const int64_t *target, const float *grad_loss,
+                                             float *grad_x, int64_t M, int64_t N, void *stream)
+{
+    clear_stale_error();
+    if (M <= 0 || N <= 0) return REPDL_E_SHAPE;
+    if (!x || !target || !grad_loss || !grad_x) return REPDL_E_NULL;
+    int64_t blocks = (M + LOSS_THREADS - 1) / LOSS_THREADS;
+    if (blocks > 0x7FFFFFFF) return REPDL_E_RANGE;
+    xent_grad_rows_kernel<<<(unsigned)blocks, LOSS_THREADS, 0, (cudaStream_t)stream>>>(
+        x, target, grad_loss, grad_x, M, N, (float)(1.0 / (double)M));
+    return launch_status();
+}
 
 extern "C" int repdl_b200_softmax(const float *x, float *y, int64_t M, int64_t N, void *stream)
 {

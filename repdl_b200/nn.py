@@ -277,10 +277,9 @@ class _CrossEntropy(torch.autograd.Function):
         logits, target = ctx.saved_tensors
         gl = None
         if ctx.needs_input_grad[0]:
-            # (softmax - one_hot) * (1/B) * g : three separately rounded steps (repdl/nn/loss.py:29-33)
-            gl = ops.softmax(logits) - torch.nn.functional.one_hot(target, logits.shape[1])
-            gl *= 1.0 / logits.shape[0]
-            gl *= g
+            # (softmax - one_hot) * (1/B) * g : three separately rounded steps (repdl/nn/loss.py:29-33),
+            # in one launch
+            gl = ops.cross_entropy_grad(logits, target, g)
         return gl, None
 
 

@@ -269,6 +269,22 @@ def cross_entropy(input: torch.Tensor, target: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def cross_entropy_grad(input: torch.Tensor, target: torch.Tensor, grad_loss: torch.Tensor) -> torch.Tensor:
+    """Gradient of cross_entropy(input, target) with respect to input, times grad_loss (a scalar tensor):
+    (softmax - one_hot) * float(1 / rows) * grad_loss with the three roundings of the reference's backward
+    (repdl/nn/loss.py:29-33), in one launch.  Class indices must be valid (torch's one_hot would raise)."""
+    x = _need(input, "input", 2).contiguous()
+    t = _need(target, "target", 1, torch.int64).contiguous()
+    if t.shape[0] != x.shape[0]:
+        raise ValueError("cross_entropy_grad: target length != rows")
+    g = _need(grad_loss.reshape(1), "grad_loss", 1).contiguous()
+    out = torch.empty_like(x)
+    with torch.cuda.device(x.device):
+        check(lib.repdl_b200_cross_entropy_grad(x.data_ptr(), t.data_ptr(), g.data_ptr(), out.data_ptr(), x.shape[0],
+                                                x.shape[1], _stream(x)), "cross_entropy_grad")
+    return out
+
+
 def _with_nvtx_ranges():
     """REPDL_B200_NVTX=1: every public operator runs inside an NVTX range named after it, so that a
     timeline profiler shows which operator each kernel belongs to (off by default: the ranges cost

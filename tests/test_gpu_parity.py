@@ -235,6 +235,20 @@ def test_mm_from_host_wave_aligned_blocks_and_column_parts(ops):
         assert torch.equal(c_host.view(torch.int32), want.cpu().view(torch.int32))
 
 
+def test_cross_entropy_gradient_in_one_launch(ops):
+    """ops.cross_entropy_grad equals the reference's backward composition (softmax, one_hot, subtraction,
+    two scalings) evaluated with the oracle's softmax on the CPU, bit for bit."""
+    g = torch.Generator().manual_seed(91)
+    for M, N, gscale in ((256, 10, 1.0), (37, 5, 0.3), (1, 1, -2.0), (300, 129, 1.0)):
+        x = torch.randn(M, N, generator=g) * 6
+        t = torch.randint(0, N, (M,), generator=g)
+        gl = torch.tensor(gscale)
+        want = oracle.softmax(x) - torch.nn.functional.one_hot(t, N)
+        want *= 1.0 / M
+        want *= gl
+        assert bits_equal(ops.cross_entropy_grad(x.cuda(), t.cuda(), gl.cuda()), want)
+
+
 def test_strided_copy_entry_point(ops):
     """repdl_b200_copy2d: a column block of a pinned host matrix to the device, device to device, and back;
     bad arguments are refused before anything is queued."""
